@@ -3,6 +3,7 @@ from .errors import ConfigError, UnknownArchitectureError
 from .mistral import MistralConfig
 from .bidinex import BidinexConfig
 from .loduzen import LoduzenConfig
+from .birepel import BirepelConfig
 from .presets import PRESETS, preset
 
 

@@ -138,14 +138,21 @@ class Kernels:
         L = self.lib
         L.braid_last_error.restype = c_char_p
         L.braid_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
-        L.braid_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
+        L.braid_embed_pos.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                      c_int, c_void_p, c_void_p]
+        L.braid_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float,
+                                    c_void_p]
+        L.braid_head_prep_kv.argtypes = [c_void_p, c_longlong, c_int] + [c_void_p] * 5 + [c_int] * 10 + \
+                                        [c_float, c_float, c_int, c_void_p, c_void_p]
+        L.braid_head_gate.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p] + [c_int] * 5 + [c_void_p]
+        L.braid_glu_clamp.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p]
         L.braid_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         L.braid_act_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         L.braid_head_norm_rope_kv.argtypes = [c_void_p, c_longlong, c_int] + [c_void_p] * 7 + [c_int] * 10 + \
                                              [c_float, c_float, c_void_p, c_void_p]
         L.braid_act_mul_gather.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
                                            c_int, c_int, c_int, c_int, c_void_p]
-        L.braid_rmsnorm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+        L.braid_rmsnorm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p]
         L.braid_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
         L.braid_rope_kv_write.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -155,7 +162,7 @@ class Kernels:
         L.braid_gather_i32.restype = c_int
         L.braid_attn_simple.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_float, c_int, c_float, c_float, c_void_p, c_void_p]
+                                        c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
         L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
         scale = [c_void_p, c_int, c_longlong, c_float, c_float]        # RowScale.args()
@@ -184,7 +191,7 @@ class Kernels:
         L.braid_concat2.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         for name in ("braid_dyt", "braid_softcap", "braid_concat2"):
             getattr(L, name).restype = c_int
-        for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_act_mul", "braid_head_norm_rope_kv",
+        for name in ("braid_embed", "braid_embed_pos", "braid_head_prep_kv", "braid_head_gate", "braid_glu_clamp", "braid_rmsnorm", "braid_silu_mul", "braid_act_mul", "braid_head_norm_rope_kv",
                      "braid_act_mul_gather", "braid_rmsnorm_add", "braid_residual_add",
                      "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
                      "braid_gemm_tc", "braid_gemm_tc2", "braid_argmax", "braid_sample", "braid_streamk_reduce",
@@ -216,7 +223,8 @@ class Kernels:
                      "tcgen05 attention gave up (a wait ran out, a visible position had no page, or its shared "
                      "memory was not 1024-byte aligned)",
                      "attention met a visible position whose page is absent or outside the cache (it read page 0 "
-                     "instead; the result is wrong)"]
+                     "instead; the result is wrong)",
+                     "a token stands at a position past the model's table of positions"]
             raise KernelError("device error: " + "; ".join(n for n, f in zip(names, flags) if f))
 
     # ------------------------------------------------------------------ row-wise kernels
@@ -233,22 +241,33 @@ class Kernels:
                                               self._stream()), "logit_hash")
         return [v & 0xFFFFFFFFFFFFFFFF for v in out[:n].tolist()]
 
-    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
-        """out[t] = table[ids[t]] * scale, float32."""
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+              pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+        """out[t] = table[ids[t]] * scale, float32; with `pos_table` ([positions, hidden], the table's element type)
+        plus pos_table[positions[t]], unscaled.  A position past the table raises the cache flag and adds nothing."""
         n, hidden = out.shape
         self.launches += 1
+        if pos_table is not None:
+            if pos_table.dtype != table.dtype or pos_table.shape[1] != hidden or not pos_table.is_contiguous() or positions is None:
+                raise KernelError("embed: the table of positions has the token table's element type and width, and needs positions")
+            self._check(self.lib.braid_embed_pos(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+                                                 n, hidden, table.shape[0], float(scale), pos_table.data_ptr(),
+                                                 positions.data_ptr(), pos_table.shape[0], self._error_flag.data_ptr() + 20,
+                                                 self._stream()), "embed")
+            return
         self._check(self.lib.braid_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
                                          n, hidden, table.shape[0], float(scale), self._stream()), "embed")
 
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float,
-                row_index: Optional[torch.Tensor] = None) -> None:
+                row_index: Optional[torch.Tensor] = None, w_offset: float = 0.0) -> None:
+        """out = x / sqrt(mean(x^2) + eps) * (w + w_offset), row by row (w_offset 1: zero-centred weights)."""
         rows, width = out.shape
         if x.dtype != torch.float32:
             raise KernelError("rmsnorm reads the float32 residual stream")
         self.launches += 1
         self._check(self.lib.braid_rmsnorm(x.data_ptr(), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
                                            dtype_code(out.dtype), _ptr(row_index), rows, width, float(eps),
-                                           self._stream()), "rmsnorm")
+                                           float(w_offset), self._stream()), "rmsnorm")
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
         self.act_mul(gu, out, "silu")
@@ -297,14 +316,54 @@ class Kernels:
                                                   dtype_code(out.dtype), rows, dim, activation_code(activation),
                                                   self._stream()), "act_mul_gather")
 
-    def rmsnorm_add(self, h: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> None:
-        """h += y / sqrt(mean(y^2) + eps) * w, row by row; h and y float32 [rows, width], contiguous."""
+    def rmsnorm_add(self, h: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, w_offset: float = 0.0) -> None:
+        """h += y / sqrt(mean(y^2) + eps) * (w + w_offset), row by row; h and y float32 [rows, width], contiguous."""
         if h.dtype != torch.float32 or y.dtype != torch.float32 or h.shape != y.shape or not h.is_contiguous() \
                 or not y.is_contiguous() or w.numel() != h.shape[1]:
             raise KernelError("rmsnorm_add: h and y are contiguous float32 of one shape, w one number a column")
         self.launches += 1
         self._check(self.lib.braid_rmsnorm_add(h.data_ptr(), y.data_ptr(), w.data_ptr(), dtype_code(w.dtype), h.shape[0],
-                                               h.shape[1], float(eps), self._stream()), "rmsnorm_add")
+                                               h.shape[1], float(eps), float(w_offset), self._stream()), "rmsnorm_add")
+
+    def head_prep_kv(self, src: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                     page_table: Optional[torch.Tensor], cache: Optional[torch.Tensor], nqh: int, nkh: int, dk: int, dv: int,
+                     hd: int, unit: bool, eps: float, temp_coef: float = 0.0, temp_every: int = 0) -> None:
+        """Rows of stacked heads without rotation (nqh query heads of dk, nkh key heads of dk, nkh value heads of dv):
+        with `unit` queries and keys are divided by their root mean square over the head; queries are multiplied by
+        1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every 0: not); queries go to q_out [rows, nqh * hd],
+        keys and values into the cache's planes, each padded with zeros up to hd."""
+        if src.stride(1) != 1 or src.shape[1] < nqh * dk + nkh * (dk + dv) or q_out.dtype != src.dtype \
+                or tuple(q_out.shape) != (src.shape[0], nqh * hd) or not q_out.is_contiguous():
+            raise KernelError("head_prep_kv: the rows do not hold the heads, or q_out is not [rows, heads * padded size]")
+        if cache is not None and (cache.dtype != src.dtype or cache.shape[-1] != hd or cache.shape[1] != 2 or cache.shape[2] != nkh):
+            raise KernelError("head_prep_kv: the cache is [pages, 2, kv_heads, page, padded size] of the rows' element type")
+        self.launches += 1
+        self._check(self.lib.braid_head_prep_kv(
+            src.data_ptr(), src.stride(0), dtype_code(src.dtype), q_out.data_ptr(), positions.data_ptr(), token_seq.data_ptr(),
+            _ptr(page_table), _ptr(cache), src.shape[0], nqh, nkh, dk, dv, hd, int(unit),
+            cache.shape[3] if cache is not None else build.page_size(), page_table.shape[1] if page_table is not None else 0,
+            cache.shape[0] if cache is not None else 0, float(eps), float(temp_coef), int(temp_every),
+            self._error_flag.data_ptr(), self._stream()), "head_prep_kv")
+
+    def head_gate(self, x: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, heads: int, hd: int, dv: int) -> None:
+        """out[r, h * dv + c] = x[r, h * hd + c] * sigmoid(gate[r, h]), c < dv (gate None: the copy alone)."""
+        rows = out.shape[0]
+        if x.stride(1) != 1 or not out.is_contiguous() or out.shape[1] != heads * dv or x.dtype != out.dtype \
+                or (gate is not None and (gate.dtype != x.dtype or gate.stride(1) != 1 or gate.shape[1] < heads)):
+            raise KernelError("head_gate: x, gate and out of one element type; out contiguous [rows, heads * dv]")
+        self.launches += 1
+        self._check(self.lib.braid_head_gate(x.data_ptr(), x.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                             out.data_ptr(), dtype_code(out.dtype), rows, heads, hd, dv, self._stream()),
+                    "head_gate")
+
+    def glu_clamp(self, gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+        """out = g * sigmoid(alpha * g) * (u + 1), g = min(gu[:, :I], limit), u = clamp(gu[:, I:], -limit, limit)."""
+        rows, inter = out.shape
+        if not gu.is_contiguous() or not out.is_contiguous() or gu.shape[1] != 2 * inter or gu.dtype != out.dtype:
+            raise KernelError("glu_clamp: gu contiguous [rows, 2 I], out contiguous [rows, I], one element type")
+        self.launches += 1
+        self._check(self.lib.braid_glu_clamp(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, inter, float(limit),
+                                             float(alpha), self._stream()), "glu_clamp")
 
     def residual_add(self, h: torch.Tensor, delta: torch.Tensor) -> None:
         self.launches += 1
@@ -336,19 +395,29 @@ class Kernels:
     def attn_simple(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                     positions: torch.Tensor, token_seq: torch.Tensor, nqh: int, nkh: int, hd: int,
                     page_size: int, window: Optional[int], scale: float, sink: Optional[float] = None,
-                    out_scale: float = 1.0) -> None:
+                    out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
+                    head_gate: Optional[torch.Tensor] = None) -> None:
         """q: [rows, >= nqh*hd] (a view of the qkv rows is fine), out: [rows, nqh*hd].  `sink`: the score of an
         attention sink, one more term of the softmax's denominator that has no value (None: no sink);
-        `out_scale`: a constant factor on the result."""
+        `head_sinks` (float32 [nqh]): a sink score a head instead; `out_scale`: a constant factor on the result;
+        `head_gate` ([rows, >= nqh] of the rows' type, a view is fine): head h's result times sigmoid(head_gate[row, h])."""
         rows = out.shape[0]
+        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype)
         self.launches += 1
         self._check(self.lib.braid_attn_simple(
             q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache.data_ptr(), page_table.data_ptr(),
             positions.data_ptr(), token_seq.data_ptr(), q.stride(0), out.stride(0), rows, nqh, nkh, hd,
             page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale),
-            int(sink is not None), float(sink or 0.0), float(out_scale),
-            self._error_flag.data_ptr() + 16, self._stream()),
+            int(sink is not None), float(sink or 0.0), float(out_scale), _ptr(head_sinks), _ptr(head_gate),
+            head_gate.stride(0) if head_gate is not None else 0, self._error_flag.data_ptr() + 16, self._stream()),
             "attn_simple")
+
+    @staticmethod
+    def _check_head_extras(head_sinks, head_gate, nqh: int, dtype) -> None:
+        if head_sinks is not None and (head_sinks.dtype != torch.float32 or head_sinks.numel() != nqh or not head_sinks.is_contiguous()):
+            raise KernelError(f"attention: a sink a head is a contiguous float32 tensor of {nqh} scores")
+        if head_gate is not None and (head_gate.dtype != dtype or head_gate.stride(1) != 1 or head_gate.shape[1] < nqh):
+            raise KernelError("attention: the heads' gates are rows of the result's element type with a column a head")
 
     @staticmethod
     def attn_mma_supports(head_dim: int) -> bool:
@@ -363,7 +432,8 @@ class Kernels:
             lib = ctypes.CDLL(str(build.attention_library(head_dim, verbose=self._verbose)))
             lib.braid_last_error.restype = c_char_p
             lib.braid_attn_mma.restype = c_int
-            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 13 + [c_float, c_int, c_float, c_float, c_void_p, c_void_p]
+            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 13 + [c_float, c_int, c_float, c_float, c_void_p, c_void_p,
+                                           c_longlong, c_void_p, c_void_p]
             lib.braid_attn_mma_partial_floats.restype = c_longlong
             lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
             lib.braid_attn_tc_supported.restype = c_int
@@ -371,7 +441,7 @@ class Kernels:
             if lib.has_tc:
                 lib.braid_attn_tc.restype = c_int
                 lib.braid_attn_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong] + [c_void_p] * 4 + [c_int] * 10 + \
-                                             [c_float, c_int, c_float, c_float, c_void_p, c_void_p]
+                                             [c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
             lib.braid_attn_mma_decode_slots.restype = c_int
             lib.braid_attn_mma_decode_slots.argtypes = [c_int]
             lib.decode_slots = lib.braid_attn_mma_decode_slots(1)     # CTAs of the few-token kernel held at once
@@ -392,10 +462,12 @@ class Kernels:
     def attn_tc(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                 q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, n_seqs: int, max_q_len: int,
                 nqh: int, nkh: int, hd: int, window: Optional[int], scale: float, sink: Optional[float] = None,
-                out_scale: float = 1.0) -> None:
-        """bfloat16 attention of prompts over the cache on tcgen05 (head sizes 64 and 128); `sink` and `out_scale`
-        as in `attn_simple`."""
+                out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
+                head_gate: Optional[torch.Tensor] = None) -> None:
+        """bfloat16 attention of prompts over the cache on tcgen05 (head sizes 64 and 128); `sink`, `head_sinks`,
+        `out_scale` and `head_gate` as in `attn_simple`."""
         lib = self.attn_mma_library(hd)
+        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype)
         self._check_pages(cache)
         if not lib.has_tc:
             raise KernelError(f"the tcgen05 attention is built for head sizes 64 and 128, not {hd}")
@@ -405,6 +477,7 @@ class Kernels:
                                q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), q.stride(0), out.stride(0),
                                out.shape[0], n_seqs, max_q_len, nqh, nkh, hd, page_table.shape[1], int(window or 0),
                                float(scale), int(sink is not None), float(sink or 0.0), float(out_scale),
+                               _ptr(head_sinks), _ptr(head_gate), head_gate.stride(0) if head_gate is not None else 0,
                                self._error_flag.data_ptr() + 12, self._stream())
         if rc != 0:
             raise KernelError(f"attn_tc: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
@@ -416,11 +489,13 @@ class Kernels:
                  q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,
                  n_seqs: int, max_q_len: int, nqh: int, nkh: int, hd: int, window: Optional[int], scale: float,
                  n_splits: int = 1, few_tokens: bool = False, sink: Optional[float] = None,
-                 out_scale: float = 1.0) -> None:
+                 out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
+                 head_gate: Optional[torch.Tensor] = None) -> None:
         """bfloat16 attention over the cache on the tensor cores; `n_splits` > 1 slices the
-        context (for steps of few tokens) and merges the slices in a second kernel.  `sink` and
-        `out_scale` as in `attn_simple` (the sink is counted once, where the slices merge)."""
+        context (for steps of few tokens) and merges the slices in a second kernel.  `sink`, `head_sinks`,
+        `out_scale` and `head_gate` as in `attn_simple` (the sink is counted once, where the slices merge)."""
         lib = self.attn_mma_library(hd)
+        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype)
         self._check_pages(cache)
         rows = out.shape[0]
         partial = None
@@ -437,7 +512,9 @@ class Kernels:
                                 q.stride(0), out.stride(0), rows, n_seqs, max_q_len, nqh, nkh, hd,
                                 page_table.shape[1], cache.shape[0], int(window or 0), n_splits,
                                 1 if few_tokens else 0, float(scale), int(sink is not None), float(sink or 0.0),
-                                float(out_scale), self._error_flag.data_ptr() + 16, self._stream())
+                                float(out_scale), _ptr(head_sinks), _ptr(head_gate),
+                                head_gate.stride(0) if head_gate is not None else 0,
+                                self._error_flag.data_ptr() + 16, self._stream())
         if rc != 0:
             raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
@@ -492,13 +569,19 @@ class Kernels:
                                                   c_void_p, c_longlong, c_longlong] + [c_void_p] * 4 + [c_int] * 5 + [c_void_p]
                 lib.braid_linear_scan.argtypes = [c_void_p, c_longlong] * 4 + [c_void_p] * 3 + [c_void_p, c_longlong] + \
                                                  [c_void_p, c_longlong, c_longlong] + [c_void_p] * 3 + [c_int] * 7 + \
-                                                 [c_float, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p]
+                                                 [c_float, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int,
+                                                  c_void_p]
+                lib.braid_mlstm_gates.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_longlong,
+                                                  c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
+                lib.braid_mlstm_out.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
+                                                c_longlong, c_void_p] + [c_int] * 4 + [c_float, c_void_p]
                 lib.braid_scan_decay.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
                 lib.braid_linear_scan_work_floats.argtypes = [c_int] * 7
                 lib.braid_linear_scan_work_floats.restype = c_longlong
                 lib.braid_gated_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong,
                                                  c_void_p] + [c_int] * 5 + [c_float, c_float, c_void_p]
-                names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm", "braid_scan_decay")
+                names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm", "braid_scan_decay", "braid_mlstm_gates",
+                         "braid_mlstm_out")
             elif name == "moe":
                 lib.braid_moe_route.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_float, c_void_p]
                 lib.braid_moe_plan.argtypes = [c_void_p] * 6 + [c_int] * 5 + [c_void_p]
@@ -634,9 +717,10 @@ class Kernels:
         return slot_pair, pair_slot, tile_expert, meta, max_tiles
 
     def moe_gemm_simt(self, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], out: torch.Tensor, plan,
-                      top: int, tile: int) -> None:
+                      top: int, tile: int, relu2: bool = False) -> None:
         """The experts' products over a plan's slots, plain.  With w1: out[slot] = silu(w0[e] x[row]) * (w1[e] x[row]),
-        x the step's rows; without: out[slot] = w0[e] x[slot], x a tensor of slots.  w0, w1 [experts, J, K]."""
+        x the step's rows; without: out[slot] = w0[e] x[slot], x a tensor of slots; with `relu2` (and no w1):
+        out[slot] = relu(w0[e] x[row])^2, x the step's rows (experts without a gate).  w0, w1 [experts, J, K]."""
         lib = self.part_library("moe")
         slot_pair, _pair_slot, tile_expert, meta, max_tiles = plan
         j, k = w0.shape[1], w0.shape[2]
@@ -649,8 +733,14 @@ class Kernels:
         self.launches += 1
         self._check_lib(lib, lib.braid_moe_gemm_simt(
             x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
-            meta.data_ptr(), dtype_code(x.dtype), 0 if w1 is not None else 1, x.stride(0), out.stride(0), j, k, top, tile,
+            meta.data_ptr(), dtype_code(x.dtype), self._moe_mode(w1, relu2), x.stride(0), out.stride(0), j, k, top, tile,
             max_tiles, self._stream()), "moe_gemm_simt")
+
+    @staticmethod
+    def _moe_mode(w1, relu2: bool) -> int:
+        if relu2 and w1 is not None:
+            raise KernelError("moe_gemm: the squared relu is the activation of experts without a gate (no w1)")
+        return 2 if relu2 else (0 if w1 is not None else 1)
 
     @staticmethod
     def moe_gemm_mma_eligible(x: torch.Tensor, w0: torch.Tensor, tile: int) -> bool:
@@ -658,7 +748,7 @@ class Kernels:
                 and x.data_ptr() % 16 == 0 and w0.data_ptr() % 16 == 0 and tile in (16, 64))
 
     def moe_gemm_mma(self, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], out: torch.Tensor, plan,
-                     top: int, tile: int) -> None:
+                     top: int, tile: int, relu2: bool = False) -> None:
         """`moe_gemm_simt` in bfloat16 on the tensor cores; the plan's tile (16 or 64 slots) is the CTA's."""
         lib = self.part_library("moe")
         slot_pair, _pair_slot, tile_expert, meta, max_tiles = plan
@@ -672,7 +762,7 @@ class Kernels:
         self.launches += 1
         self._check_lib(lib, lib.braid_moe_gemm_mma(
             x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
-            meta.data_ptr(), 0 if w1 is not None else 1, x.stride(0), out.stride(0), j, k, top, tile, max_tiles,
+            meta.data_ptr(), self._moe_mode(w1, relu2), x.stride(0), out.stride(0), j, k, top, tile, max_tiles,
             self._stream()), "moe_gemm_mma")
 
     @staticmethod
@@ -778,13 +868,18 @@ class Kernels:
     def linear_scan(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, gate_bias: torch.Tensor,
                     out: torch.Tensor, state: torch.Tensor, state_offset: int, ctx, heads: int, groups: int, dk: int,
                     dv: int, mode: str, q_scale: float = 1.0, inv_tau: float = 1.0, a_log: Optional[torch.Tensor] = None,
-                    skip: Optional[torch.Tensor] = None, chunk: Optional[int] = None, gate_is_decay: bool = False) -> None:
+                    skip: Optional[torch.Tensor] = None, chunk: Optional[int] = None, gate_is_decay: bool = False,
+                    kappa: Optional[torch.Tensor] = None, v_cols: Optional[int] = None) -> None:
         """The recurrence S <- diag(a) S + (kappa k) v^T, o = S^T (q_scale q) + skip v, token by token along each
         sequence of the step, S float32 [heads, dk, dv] at `state_offset` bytes of each slot.  mode "channel":
         a = sigmoid(gate + gate_bias)^inv_tau per key channel (gate float32 [rows, heads * dk]); mode "head":
         dt = softplus(gate + gate_bias), a = exp(-exp(a_log) dt), kappa = dt (gate [rows, heads] in the run's
         type).  q, k [rows, groups * dk], v [rows, heads * dv] (views are fine); out float32 [rows, heads * dv].
         `gate_is_decay` (mode "channel"): `gate` holds the decays themselves, as `scan_decay` left them.
+        mode "given": a = gate[row, head] and kappa = kappa[row, head], float32 views of one row stride, worked out
+        before (`mlstm_gates`); with `v_cols` < dv, v holds v_cols columns a head and the state's other columns take
+        a value of 1 (a normaliser: S[:, v_cols] sums the decayed keys, out[:, v_cols] is its product with the query).
+        `gate_bias` is then unused (pass any tensor of the rows' type).
         A step whose longest sequence brings at least two chunks of `chunk` tokens (default: see SCAN_CHUNK; 0: never)
         walks its chunks side by side in three passes (see csrc/scan.cu); the results differ from the walk
         token by token by rounding only."""
@@ -800,12 +895,19 @@ class Kernels:
                     or a_log.dtype != q.dtype or (skip is not None and skip.dtype != q.dtype):
                 raise KernelError("linear_scan: a decay per head takes a gate [rows, heads], its bias, A_log and a skip "
                                   "of the rows' element type")
+        elif mode == "given":
+            if gate.dtype != torch.float32 or kappa is None or kappa.dtype != torch.float32 or kappa.stride(0) != gate.stride(0) \
+                    or kappa.stride(1) != 1 or gate.shape[1] < heads or kappa.shape[1] < heads:
+                raise KernelError("linear_scan: given decays and key factors are float32 [rows, heads] views of one row stride")
         else:
             raise KernelError(f"linear_scan: unknown decay mode {mode!r}")
+        vc = dv if v_cols is None else int(v_cols)
+        if v.shape[1] < heads * vc or out.shape[1] < heads * dv:
+            raise KernelError("linear_scan: v or out does not hold the heads' columns")
         if chunk is None:
             chunk = SCAN_CHUNK if SCAN_CHUNK is not None else (128 if int(ctx.max_q_len) >= 1024 else 64)
         chunk = int(chunk)
-        code = 0 if mode == "channel" else 1
+        code = {"channel": 0, "head": 1, "given": 2}[mode]
         need = lib.braid_linear_scan_work_floats(ctx.n_seqs, int(ctx.max_q_len), chunk, heads, dk, dv, code)
         work = torch.empty(need, dtype=torch.float32, device=out.device) if need > 0 else None
         self.launches += 3 if need > 0 else 1
@@ -814,7 +916,42 @@ class Kernels:
             gate_bias.data_ptr(), _ptr(a_log), _ptr(skip), out.data_ptr(), out.stride(0),
             *self._state_args(state, state_offset), ctx.q_start.data_ptr(), ctx.q_len.data_ptr(), ctx.slot_ids.data_ptr(),
             dtype_code(q.dtype), code, ctx.n_seqs, heads, groups, dk, dv, float(q_scale),
-            float(inv_tau), int(ctx.max_q_len), chunk, _ptr(work), need, int(gate_is_decay), self._stream()), "linear_scan")
+            float(inv_tau), int(ctx.max_q_len), chunk, _ptr(work), need, int(gate_is_decay), _ptr(kappa), vc,
+            self._stream()), "linear_scan")
+
+    def mlstm_gates(self, z: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, out: torch.Tensor,
+                    state: torch.Tensor, state_offset: int, ctx, heads: int, cap: float) -> None:
+        """The gates of a matrix memory along each sequence of the step.  z float32 [rows, 2 heads]: the logits of the
+        input gates, then of the forget gates (biases [heads] each).  li = cap tanh((zi + bi) / cap),
+        lf = log sigmoid(cap tanh((zf + bf) / cap)); m_t = max(lf + m_(t-1), li) with m float32 [heads] at
+        `state_offset` bytes of each slot (0 for a new sequence).  out float32 [rows, 3 heads]: exp(lf + m_(t-1) - m_t),
+        exp(li - m_t), exp(-m_t)."""
+        lib = self.part_library("scan")
+        if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < 2 * heads or out.dtype != torch.float32 \
+                or not out.is_contiguous() or tuple(out.shape) != (z.shape[0], 3 * heads) or bias_i.dtype != bias_f.dtype \
+                or bias_i.numel() != heads or bias_f.numel() != heads:
+            raise KernelError("mlstm_gates: z float32 [rows, 2 heads], out contiguous float32 [rows, 3 heads], a bias a head")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_mlstm_gates(
+            z.data_ptr(), z.stride(0), bias_i.data_ptr(), bias_f.data_ptr(), dtype_code(bias_i.dtype), out.data_ptr(),
+            *self._state_args(state, state_offset), ctx.q_start.data_ptr(), ctx.q_len.data_ptr(), ctx.slot_ids.data_ptr(),
+            ctx.n_seqs, heads, float(cap), self._stream()), "mlstm_gates")
+
+    def mlstm_out(self, y: torch.Tensor, floors: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                  token_seq: torch.Tensor, heads: int, dv: int, eps: float) -> None:
+        """The read-out of a matrix memory: y float32 [rows, heads * (dv + 1)] (a head's S^T q, then n . q);
+        o = y[:dv] / (max(|n . q|, floors[row, head]) + 1e-6); out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate),
+        w [heads * dv], gate and out [rows, heads * dv] in the run's type (views are fine)."""
+        lib = self.part_library("scan")
+        rows = y.shape[0]
+        if y.dtype != torch.float32 or not y.is_contiguous() or y.shape[1] != heads * (dv + 1) or floors.dtype != torch.float32 \
+                or floors.stride(1) != 1 or not (gate.dtype == w.dtype == out.dtype) or gate.stride(1) != 1 or out.stride(1) != 1 \
+                or w.numel() != heads * dv or gate.shape[1] < heads * dv or out.shape[1] < heads * dv:
+            raise KernelError("mlstm_out: y contiguous float32 [rows, heads * (dv + 1)]; gate, w, out of one element type")
+        self.launches += 1
+        self._check_lib(lib, lib.braid_mlstm_out(
+            y.data_ptr(), floors.data_ptr(), floors.stride(0), gate.data_ptr(), gate.stride(0), w.data_ptr(), out.data_ptr(),
+            out.stride(0), token_seq.data_ptr(), dtype_code(out.dtype), rows, heads, dv, float(eps), self._stream()), "mlstm_out")
 
     def scan_decay(self, z: torch.Tensor, bias: torch.Tensor, inv_tau: float) -> None:
         """z <- sigmoid(z + bias)^inv_tau in place (z float32 [rows, n]): the decays of a recurrence from their logits,

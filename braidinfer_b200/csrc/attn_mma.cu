@@ -43,6 +43,9 @@ struct AttnMmaArgs {
     int has_sink;                // the denominator counts one more term 2^sink_log2 that has no value (an attention sink)
     float sink_log2;             // the sink's score * log2(e)
     float out_scale;             // a constant factor on the result
+    const float* head_sinks;     // [nqh] float32 natural-log scores: a sink a head (learned) instead of the one score; or null
+    const __nv_bfloat16* head_gate;  // [rows, gate_stride]: head h's result is multiplied by sigmoid(head_gate[row, h]); or null
+    long long gate_stride;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -286,11 +289,13 @@ attn_mma_kernel(AttnMmaArgs a) {
         if (a.n_splits == 1) {
             float corr = 1.f;
             if (a.has_sink) {                            // the sink joins as one more score, with no value
-                const float mn = fmaxf(m, a.sink_log2);
+                const float sk = a.head_sinks ? a.head_sinks[head] * 1.4426950408889634f : a.sink_log2;
+                const float mn = fmaxf(m, sk);
                 corr = exp2f(m - mn);                    // exp2(-inf) = 0
-                l = l * corr + exp2f(a.sink_log2 - mn);
+                l = l * corr + exp2f(sk - mn);
             }
-            const float inv = corr * a.out_scale / l;
+            float inv = corr * a.out_scale / l;
+            if (a.head_gate) inv *= 1.f / (1.f + __expf(-__bfloat162float(a.head_gate[grow * a.gate_stride + head])));
             __nv_bfloat16* dst = a.out + grow * a.out_row_stride + (size_t)head * HD + (lane & 3) * 2;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i)
@@ -312,13 +317,16 @@ attn_mma_kernel(AttnMmaArgs a) {
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                     const int* __restrict__ token_seq, int out_row_stride, int nqh, int n_splits,
-                                    int has_sink, float sink_log2, float out_scale) {
+                                    int has_sink, float sink_log2, float out_scale, const float* __restrict__ head_sinks,
+                                    const __nv_bfloat16* __restrict__ head_gate, long long gate_stride) {
     pdl_trigger();
     // the step's tables are on the device before the step's first kernel: read before the wait
     const int row = blockIdx.x, head = blockIdx.y;
     const bool padding = token_seq[row] < 0;
+    if (head_sinks) sink_log2 = head_sinks[head] * 1.4426950408889634f;
     pdl_wait();
     if (padding) return;
+    const float gate = head_gate ? 1.f / (1.f + __expf(-__bfloat162float(head_gate[(size_t)row * gate_stride + head]))) : 1.f;
     const float* p = partial + ((size_t)row * nqh + head) * n_splits * (HD + 2);
     constexpr int B = 16;                                  // slices asked for at once: one trip for up to 16
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
@@ -354,7 +362,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bflo
             L = L * c + exp2f(sink_log2 - Mn);
             acc *= c;
         }
-        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * out_scale / L);
+        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * (out_scale * gate) / L);
     }
 }
 
@@ -405,8 +413,12 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
                               const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
                               int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
                               int nqh, int nkh, int hd, int table_cols, int num_pages, int window, int n_splits, int kind,
-                              float scale, int has_sink, float sink_score, float out_scale, int* error_flag, void* stream) {
+                              float scale, int has_sink, float sink_score, float out_scale, const float* head_sinks,
+                              const void* head_gate, long long gate_stride, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
+    if (head_sinks) has_sink = 1;
+    // a gate a head rides on the last kernel that touches a row: the merge of the slices, or the attention itself
+    const __nv_bfloat16* gate_here = n_splits > 1 ? nullptr : (const __nv_bfloat16*)head_gate;
     if (!error_flag) BRAID_REFUSE("attn_mma: error_flag is required");
     if (num_pages <= 0 || table_cols <= 0) BRAID_REFUSE("attn_mma: the cache has no pages (pages=%d, table columns=%d)", num_pages, table_cols);
     if (hd != BRAID_HD) BRAID_REFUSE("attn_mma: this library was compiled for head_dim=%d, not %d", BRAID_HD, hd);
@@ -417,7 +429,8 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     if (n_splits > 1 && !partial) BRAID_REFUSE("attn_mma: n_splits > 1 needs the partial buffer");
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (float*)partial, (const __nv_bfloat16*)cache, page_table,
                   q_start, q_len, kv_before, q_row_stride, out_row_stride, nqh, nkh, table_cols, window, n_splits,
-                  scale * 1.4426950408889634f, num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale};
+                  scale * 1.4426950408889634f, num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale,
+                  head_sinks, gate_here, gate_stride};
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
@@ -425,7 +438,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     if (rc) return rc;
     if (n_splits > 1) {
         dim3 grid(rows, nqh);
-        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits, has_sink, sink_score * 1.4426950408889634f, out_scale);
+        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits, has_sink, sink_score * 1.4426950408889634f, out_scale, head_sinks, (const __nv_bfloat16*)head_gate, gate_stride);
         BRAID_LAUNCH_CHECK();
     }
     return BRAID_OK;
@@ -472,5 +485,5 @@ extern "C" int braid_attn_mma_noalloc(const void* q, void* out, const void* cach
     }
     return braid_attn_mma(q, out, n_splits > 1 ? g_noalloc_ptr[dev] : nullptr, cache, page_table, q_start, q_len,
                           kv_before, token_seq, q_row_stride, out_row_stride, rows, n_seqs, max_q_len, nqh, nkh, hd,
-                          table_cols, num_pages, window, n_splits, kind, scale, 0, 0.f, 1.f, error_flag, stream);
+                          table_cols, num_pages, window, n_splits, kind, scale, 0, 0.f, 1.f, nullptr, nullptr, 0, error_flag, stream);
 }

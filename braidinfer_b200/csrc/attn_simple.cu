@@ -10,7 +10,7 @@
 // denominator d and accumulator acc; out = acc / d.  Key j is visible to the query at
 // position p iff j <= p and, with a window w > 0, p - j < w (the window is this
 // library's own; the reference has none).  Scores, softmax and accumulation are float32.
-// With has_sink, the denominator also counts one more term exp(sink_score) that has no value
+// With has_sink (or head_sinks, a score a head), the denominator also counts one more term exp(sink_score) that has no value
 // (an attention sink: p_j = exp(s_j) / (exp(sink_score) + sum_i exp(s_i))).  out_scale is a
 // constant factor on the result.
 #include "common.cuh"
@@ -28,6 +28,9 @@ struct AttnSimpleArgs {
     int has_sink;
     float sink_score, out_scale;
     int* error_flag;          // raised when a visible position has no page, or one outside the cache
+    const float* head_sinks;  // [nqh] float32: a sink score a head (learned), instead of the one score; or null
+    const void* head_gate;    // [rows, gate_stride] in the rows' type: the result of head h is multiplied by
+    long long gate_stride;    // sigmoid(head_gate[row, h]); or null
 };
 
 #define ATTN_SIMPLE_WARPS 4
@@ -106,11 +109,13 @@ attn_simple_kernel(AttnSimpleArgs a) {
     }
     float corr_end = 1.f;
     if (a.has_sink) {                                // the sink joins as one more score, with no value
-        const float m_new = fmaxf(m, a.sink_score);
+        const float sink = a.head_sinks ? a.head_sinks[head] : a.sink_score;
+        const float m_new = fmaxf(m, sink);
         corr_end = (m == -INFINITY) ? 0.f : expf(m - m_new);
-        l = l * corr_end + expf(a.sink_score - m_new);
+        l = l * corr_end + expf(sink - m_new);
     }
-    const float inv = corr_end * a.out_scale / l;
+    float inv = corr_end * a.out_scale / l;
+    if (a.head_gate) inv *= 1.f / (1.f + expf(-to_f32(((const T*)a.head_gate)[(size_t)row * a.gate_stride + head])));
 #pragma unroll
     for (int i = 0; i < ATTN_SIMPLE_MAX_HD / 32; ++i) {
         const int d = lane + 32 * i;
@@ -122,15 +127,15 @@ extern "C" int braid_attn_simple(const void* q, void* out, int dtype, const void
                                  const int* page_table, const int* positions, const int* token_seq,
                                  int q_row_stride, int out_row_stride, int rows, int nqh, int nkh, int hd,
                                  int page_size, int table_cols, int num_pages, int window, float scale,
-                                 int has_sink, float sink_score, float out_scale,
-                                 int* error_flag, void* stream) {
+                                 int has_sink, float sink_score, float out_scale, const float* head_sinks,
+                                 const void* head_gate, long long gate_stride, int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (!error_flag) BRAID_REFUSE("attn_simple: error_flag is required");
     if (num_pages <= 0 || table_cols <= 0 || page_size <= 0) BRAID_REFUSE("attn_simple: the cache has no pages (pages=%d, table columns=%d, page size=%d)", num_pages, table_cols, page_size);
     if (nqh <= 0 || nkh <= 0 || nqh % nkh != 0) BRAID_REFUSE("attn_simple: %d query heads do not divide into %d kv heads", nqh, nkh);
     if (hd <= 0 || hd > ATTN_SIMPLE_MAX_HD) BRAID_REFUSE("attn_simple: head_dim=%d outside (0, %d]", hd, ATTN_SIMPLE_MAX_HD);
     AttnSimpleArgs a{q, out, cache, page_table, positions, token_seq, q_row_stride, out_row_stride,
-                     rows, nqh, nkh, hd, page_size, table_cols, num_pages, window, scale, has_sink, sink_score, out_scale, error_flag};
+                     rows, nqh, nkh, hd, page_size, table_cols, num_pages, window, scale, has_sink || head_sinks != nullptr, sink_score, out_scale, error_flag, head_sinks, head_gate, gate_stride};
     const long long items = (long long)rows * nqh;
     const long long blocks = (items + ATTN_SIMPLE_WARPS - 1) / ATTN_SIMPLE_WARPS;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("attn_simple: %lld (token, head) pairs exceed one launch", items);

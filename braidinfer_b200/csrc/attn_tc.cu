@@ -161,6 +161,9 @@ struct AttnTcArgs {
     int has_sink;                // the denominator counts one more term 2^sink_log2 that has no value (an attention sink)
     float sink_log2;             // the sink's score * log2(e)
     float out_scale;             // a constant factor on the result
+    const float* head_sinks;     // [nqh] float32 natural-log scores: a sink a head (learned) instead of the one score; or null
+    const __nv_bfloat16* head_gate;  // [rows, gate_stride]: head h's result is multiplied by sigmoid(head_gate[row, h]); or null
+    long long gate_stride;
 };
 
 __global__ void __launch_bounds__(FA_THREADS, 2)
@@ -424,7 +427,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 tc_fence_after();
                 // the sink joins the sum where the row is finished: l counts in units of 2^m; a sink far above every
                 // score makes the sum infinite and the row zero, which is the limit
-                const float inv = a.out_scale / (a.has_sink ? l + exp2f(a.sink_log2 - m) : l);
+                const float sk = (a.head_sinks && valid) ? a.head_sinks[head0 + hl] * 1.4426950408889634f : a.sink_log2;
+                float inv = a.out_scale / (a.has_sink ? l + exp2f(sk - m) : l);
+                if (a.head_gate && valid)
+                    inv *= 1.f / (1.f + __expf(-__bfloat162float(a.head_gate[(size_t)(q_start + tok0 + tl) * a.gate_stride + head0 + hl])));
                 __nv_bfloat16* dst = a.out + (size_t)(q_start + tok0 + tl) * a.out_row_stride + (size_t)(head0 + hl) * HD;
 #pragma unroll
                 for (int h = 0; h < HD / 64; ++h) {
@@ -464,8 +470,10 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
                              const int* q_start, const int* q_len, const int* kv_before,
                              int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
                              int nqh, int nkh, int hd, int table_cols, int window, float scale,
-                             int has_sink, float sink_score, float out_scale, int* error_flag, void* stream) {
+                             int has_sink, float sink_score, float out_scale, const float* head_sinks, const void* head_gate,
+                             long long gate_stride, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
+    if (head_sinks) has_sink = 1;
     if (hd != BRAID_HD) BRAID_REFUSE("attn_tc: this library was compiled for head_dim=%d, not %d", BRAID_HD, hd);
     if (nqh <= 0 || nkh <= 0 || nqh % nkh) BRAID_REFUSE("attn_tc: %d query heads do not divide into %d kv heads", nqh, nkh);
     if ((q_row_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) BRAID_REFUSE("attn_tc: queries and cache must be 16-byte aligned");
@@ -507,7 +515,8 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
         BRAID_REFUSE("attn_tc: the step exceeds the grid limits (%lld token tiles, %d sequences)", gx, n_seqs);
     const long long num_pages = cache_rows / (2LL * nkh * FA_PAGE);
     AttnTcArgs a{(__nv_bfloat16*)out, page_table, q_start, q_len, kv_before, out_row_stride, nqh, nkh, table_cols, window,
-                 scale * 1.4426950408889634f, (int)num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale};
+                 scale * 1.4426950408889634f, (int)num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale,
+                 head_sinks, (const __nv_bfloat16*)head_gate, gate_stride};
     braid_launch(attn_tc_kernel, dim3(nkh * hchunks, n_seqs, (unsigned)gx), dim3(FA_THREADS), FA_SMEM,
                  (cudaStream_t)stream, mq, mkv, a);
     BRAID_LAUNCH_CHECK();

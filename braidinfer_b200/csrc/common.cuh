@@ -88,6 +88,12 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
     return 0.5f * z * (1.f + tanhf(u));
 }
 __device__ __forceinline__ float silu_f32(float z) { return z / (1.f + expf(-z)); }
+// The clamped gated unit: g = min(gate, limit), u = clamp(up, -limit, limit); g * sigmoid(alpha * g) * (u + 1).
+__device__ __forceinline__ float glu_clamp_f32(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
 __device__ __forceinline__ float glu_act(float g, int act) {
     return act == BRAID_ACT_GELU_TANH ? gelu_tanh_f32(g) : silu_f32(g);
 }

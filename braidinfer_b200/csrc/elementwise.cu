@@ -15,7 +15,8 @@
 // ------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int n_tokens, int hidden, int vocab, float scale) {
+                             float* __restrict__ out, int n_tokens, int hidden, int vocab, float scale,
+                             const T* __restrict__ pos_table, const int* __restrict__ positions, int max_pos, int* error_flag) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -24,6 +25,16 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const bool valid = (id >= 0 && id < vocab);
     const T* row = table + (size_t)(valid ? id : 0) * hidden;
     float* o = out + (size_t)t * hidden;
+    if (pos_table) {
+        // a learned vector a position, added unscaled in float32; a position past the table adds nothing and is flagged
+        const int p = positions[t];
+        const bool pv = p >= 0 && p < max_pos;
+        if (!pv && valid && threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+        const T* prow = pos_table + (size_t)(pv ? p : 0) * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            o[i] = valid ? to_f32(row[i]) * scale + (pv ? to_f32(prow[i]) : 0.f) : 0.f;
+        return;
+    }
     // rows that start on 16 bytes and hold a whole number of 16-byte groups go group by group
     constexpr int VEC = 16 / sizeof(T);
     if (valid && hidden % VEC == 0 && (((uintptr_t)row | (uintptr_t)o) & 15) == 0) {
@@ -39,16 +50,27 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = valid ? to_f32(row[i]) * scale : 0.f;
 }
 
+extern "C" int braid_embed_pos(const void* table, int table_dtype, const int* ids, float* out, int n_tokens, int hidden,
+                               int vocab, float scale, const void* pos_table, const int* positions, int max_pos,
+                               int* error_flag, void* stream);
 extern "C" int braid_embed(const void* table, int table_dtype, const int* ids, float* out,
                            int n_tokens, int hidden, int vocab, float scale, void* stream) {
+    return braid_embed_pos(table, table_dtype, ids, out, n_tokens, hidden, vocab, scale, nullptr, nullptr, 0, nullptr, stream);
+}
+
+// The same with a second table [max_pos, hidden] of the table's element type: out[t] = table[ids[t]] * scale + pos_table[positions[t]].
+extern "C" int braid_embed_pos(const void* table, int table_dtype, const int* ids, float* out, int n_tokens, int hidden,
+                               int vocab, float scale, const void* pos_table, const int* positions, int max_pos,
+                               int* error_flag, void* stream) {
     if (n_tokens <= 0) return BRAID_OK;
+    if (pos_table && (!positions || max_pos <= 0)) BRAID_REFUSE("embed: a table of positions needs the rows' positions and its length");
     if (hidden <= 0 || vocab <= 0) BRAID_REFUSE("embed: hidden=%d vocab=%d must be positive", hidden, vocab);
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == BRAID_F32)
-        braid_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, n_tokens, hidden, vocab, scale);
+        braid_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, n_tokens, hidden, vocab, scale, (const float*)pos_table, positions, max_pos, error_flag);
     else if (table_dtype == BRAID_BF16)
-        braid_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, scale);
+        braid_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, scale, (const __nv_bfloat16*)pos_table, positions, max_pos, error_flag);
     else
         BRAID_REFUSE("embed: unknown table dtype code %d", table_dtype);
     BRAID_LAUNCH_CHECK();
@@ -57,9 +79,10 @@ extern "C" int braid_embed(const void* table, int table_dtype, const int* ids, f
 // ------------------------------------------------------------------ rmsnorm
 // One block per output row.  `row_index` (may be null) picks the input row of each
 // output row, which gathers the rows whose logits are wanted before the final norm.
+// `w_offset` is added to every weight in float32 (1 for zero-centred weights).
 template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                               const int* __restrict__ row_index, int rows, int width, float eps) {
+                               const int* __restrict__ row_index, int rows, int width, float eps, float w_offset) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
@@ -79,7 +102,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
     }
     ss = block_sum(ss, red);
     const float scale = rsqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * scale * to_f32(w[i]));
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * scale * (to_f32(w[i]) + w_offset));
 }
 
 // Rows whose width is a multiple of 4 (and at most 4 * 8 * 512): one pass over x with
@@ -87,7 +110,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 template <typename TW, typename TO, int PER>
 __global__ void __launch_bounds__(512)
 rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                   const int* __restrict__ row_index, int rows, int width, float eps) {
+                   const int* __restrict__ row_index, int rows, int width, float eps, float w_offset) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
@@ -119,8 +142,8 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __
         const int g = threadIdx.x + i * blockDim.x;
         if (g < groups) {
             const int c = g * 4;
-            const float y0 = v[i].x * scale * to_f32(w[c]), y1 = v[i].y * scale * to_f32(w[c + 1]);
-            const float y2 = v[i].z * scale * to_f32(w[c + 2]), y3 = v[i].w * scale * to_f32(w[c + 3]);
+            const float y0 = v[i].x * scale * (to_f32(w[c]) + w_offset), y1 = v[i].y * scale * (to_f32(w[c + 1]) + w_offset);
+            const float y2 = v[i].z * scale * (to_f32(w[c + 2]) + w_offset), y3 = v[i].w * scale * (to_f32(w[c + 3]) + w_offset);
             if (sizeof(TO) == 2) {
                 __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
                 uint2 pk;
@@ -135,7 +158,7 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __
 }
 
 extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
-                             const int* row_index, int rows, int width, float eps, void* stream) {
+                             const int* row_index, int rows, int width, float eps, float w_offset, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (width <= 0) BRAID_REFUSE("rmsnorm: width=%d must be positive", width);
     cudaStream_t s = (cudaStream_t)stream;
@@ -145,10 +168,10 @@ extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* o
         const int per = (width / 4 + threads - 1) / threads;          // float4 groups a thread
 #define BRAID_RMSV(TW, TO)                                                                                           \
         do {                                                                                                         \
-            if (per <= 1) braid_launch(rmsnorm_vec_kernel<TW, TO, 1>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
-            else if (per <= 2) braid_launch(rmsnorm_vec_kernel<TW, TO, 2>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
-            else if (per <= 4) braid_launch(rmsnorm_vec_kernel<TW, TO, 4>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
-            else braid_launch(rmsnorm_vec_kernel<TW, TO, 8>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
+            if (per <= 1) braid_launch(rmsnorm_vec_kernel<TW, TO, 1>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps, w_offset); \
+            else if (per <= 2) braid_launch(rmsnorm_vec_kernel<TW, TO, 2>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps, w_offset); \
+            else if (per <= 4) braid_launch(rmsnorm_vec_kernel<TW, TO, 4>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps, w_offset); \
+            else braid_launch(rmsnorm_vec_kernel<TW, TO, 8>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps, w_offset); \
         } while (0)
         if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_RMSV(float, float);
         else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_RMSV(float, __nv_bfloat16);
@@ -158,7 +181,7 @@ extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* o
 #undef BRAID_RMSV
         BRAID_LAUNCH_CHECK();
     }
-#define BRAID_RMS(TW, TO) braid_launch(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps)
+#define BRAID_RMS(TW, TO) braid_launch(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps, w_offset)
     if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_RMS(float, float);
     else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_RMS(float, __nv_bfloat16);
     else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) BRAID_RMS(__nv_bfloat16, float);
@@ -769,5 +792,153 @@ extern "C" int braid_logit_hash(const float* logits, long long ld, int rows, int
     if (rows <= 0) return BRAID_OK;
     if (vocab <= 0 || ld < vocab) BRAID_REFUSE("logit_hash: vocab=%d, row stride=%lld", vocab, ld);
     braid_launch(logit_hash_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ heads without rotation: norm, temperature, cache write
+// Rows of stacked heads [rows, row_stride]: nqh query heads of dk numbers, then nkh key heads of dk, then nkh value
+// heads of dv.  With `unit`, every query and key head is divided by its root mean square, sqrt(mean(x^2) + eps)
+// (no weight).  A query is then multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1), p the row's
+// position (temp_every = 0: no such factor).  Queries go to q_out [rows, nqh * hd] and keys and values into the
+// cache's planes [page][2][nkh][page_size][hd], all padded with zeros from their own size up to hd (a head size that
+// the attention kernels take); zeros change neither a score nor a result's first dv numbers.  Padding rows get zero
+// queries and write no cache.  One warp a (row, head); float32 arithmetic.
+struct HeadPrepArgs {
+    const void* src; long long row_stride;
+    void* q_out;
+    const int* positions; const int* token_seq; const int* page_table;
+    void* cache;
+    int rows, nqh, nkh, dk, dv, hd, unit;
+    int page_size, table_cols, num_pages;
+    float eps, temp_coef; int temp_every;
+    int* error_flag;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_prep_kv_kernel(HeadPrepArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = a.nqh + 2 * a.nkh;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)a.rows * heads) return;
+    const int row = (int)(item / heads), head = (int)(item - (long long)row * heads);
+    const int seq = a.token_seq[row];
+    const bool is_q = head < a.nqh, is_k = !is_q && head < a.nqh + a.nkh;
+    if (seq < 0) {
+        if (is_q) {
+            T* o = (T*)a.q_out + ((size_t)row * a.nqh + head) * a.hd;
+            for (int c = lane; c < a.hd; c += 32) o[c] = from_f32<T>(0.f);
+        }
+        return;
+    }
+    const int d = is_q || is_k ? a.dk : a.dv;
+    const size_t col0 = is_q ? (size_t)head * a.dk
+                      : is_k ? (size_t)a.nqh * a.dk + (size_t)(head - a.nqh) * a.dk
+                             : (size_t)(a.nqh + a.nkh) * a.dk + (size_t)(head - a.nqh - a.nkh) * a.dv;
+    const T* src = (const T*)a.src + (size_t)row * a.row_stride + col0;
+    const int pos = a.positions[row];
+    float f = 1.f;
+    if ((is_q || is_k) && a.unit) {
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) { const float v = to_f32(src[c]); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        f = 1.f / sqrtf(ss / (float)d + a.eps);
+    }
+    if (is_q && a.temp_every > 0) f *= 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
+    T* dst = nullptr;
+    if (is_q) {
+        dst = (T*)a.q_out + ((size_t)row * a.nqh + head) * a.hd;
+    } else if (a.cache) {
+        const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (lane == 0) atomicExch(a.error_flag, 1);
+            return;
+        }
+        dst = (T*)a.cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * a.nkh + kvh) * a.page_size + off) * a.hd;
+    }
+    if (!dst) return;
+    for (int c = lane; c < a.hd; c += 32) dst[c] = from_f32<T>(c < d ? to_f32(src[c]) * f : 0.f);
+}
+
+extern "C" int braid_head_prep_kv(const void* src, long long row_stride, int dtype, void* q_out, const int* positions,
+                                  const int* token_seq, const int* page_table, void* cache, int rows, int nqh, int nkh,
+                                  int dk, int dv, int hd, int unit, int page_size, int table_cols, int num_pages, float eps,
+                                  float temp_coef, int temp_every, int* error_flag, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (nqh <= 0 || nkh <= 0 || dk <= 0 || dv <= 0 || hd < dk || hd < dv)
+        BRAID_REFUSE("head_prep_kv: heads %d/%d of sizes %d and %d do not fit a padded head of %d", nqh, nkh, dk, dv, hd);
+    if (cache && !page_table) BRAID_REFUSE("head_prep_kv: a cache write needs the step's page table");
+    HeadPrepArgs a{src, row_stride, q_out, positions, token_seq, page_table, cache, rows, nqh, nkh, dk, dv, hd, unit,
+                   page_size, table_cols, num_pages, eps, temp_coef, temp_every, error_flag};
+    const long long blocks = ((long long)rows * (nqh + 2 * nkh) + 3) / 4;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_prep_kv: %d rows exceed one launch", rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32) braid_launch(head_prep_kv_kernel<float>, dim3((int)blocks), dim3(128), 0, s, a);
+    else if (dtype == BRAID_BF16) braid_launch(head_prep_kv_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(128), 0, s, a);
+    else BRAID_REFUSE("head_prep_kv: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ a gate a head on attention's result
+// out[r, h * dv + c] = x[r, h * hd + c] * sigmoid(gate[r, h]) for c < dv: the first dv numbers of every padded head,
+// times the head's gate (gate: a column block of the stacked projection, row stride gate_stride; null: no gate).
+template <typename T>
+__global__ void head_gate_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ gate, long long gate_stride,
+                                 T* __restrict__ out, long long total, int heads, int hd, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int per_row = heads * dv;
+    const long long r = i / per_row;
+    const int rem = (int)(i - r * per_row), h = rem / dv, c = rem - h * dv;
+    float v = to_f32(x[r * x_stride + (size_t)h * hd + c]);
+    if (gate) v *= 1.f / (1.f + expf(-to_f32(gate[r * gate_stride + h])));
+    out[i] = from_f32<T>(v);
+}
+
+extern "C" int braid_head_gate(const void* x, long long x_stride, const void* gate, long long gate_stride, void* out,
+                               int dtype, int rows, int heads, int hd, int dv, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (heads <= 0 || dv <= 0 || hd < dv) BRAID_REFUSE("head_gate: %d heads of %d numbers in heads of %d", heads, dv, hd);
+    const long long total = (long long)rows * heads * dv, blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_gate: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32)
+        braid_launch(head_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)x, x_stride, (const float*)gate,
+                     gate_stride, (float*)out, total, heads, hd, dv);
+    else if (dtype == BRAID_BF16)
+        braid_launch(head_gate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)x, x_stride,
+                     (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, total, heads, hd, dv);
+    else BRAID_REFUSE("head_gate: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ the clamped gated unit
+// gu is [rows, 2 * inter]: gate in columns [0, inter), up in [inter, 2 * inter).
+// g = min(gate, limit), u = clamp(up, -limit, limit); out = g * sigmoid(alpha * g) * (u + 1).
+template <typename T>
+__global__ void glu_clamp_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter, float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / inter;
+    const int c = (int)(i - r * inter);
+    out[i] = from_f32<T>(glu_clamp_f32(to_f32(gu[r * 2 * inter + c]), to_f32(gu[r * 2 * inter + inter + c]), limit, alpha));
+}
+
+extern "C" int braid_glu_clamp(const void* gu, void* out, int dtype, int rows, int inter, float limit, float alpha, void* stream) {
+    if (rows <= 0 || inter <= 0) return BRAID_OK;
+    const long long total = (long long)rows * inter, blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("glu_clamp: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32) braid_launch(glu_clamp_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)gu, (float*)out, total, inter, limit, alpha);
+    else if (dtype == BRAID_BF16) braid_launch(glu_clamp_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter, limit, alpha);
+    else BRAID_REFUSE("glu_clamp: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }

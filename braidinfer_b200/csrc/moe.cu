@@ -180,7 +180,8 @@ extern "C" int braid_moe_plan(const int* idx, const int* token_seq, int* slot_pa
 // ------------------------------------------------------------------ the experts' products, plain
 // Units of 16 slots x 64 outputs; 256 threads, each one slot and four outputs; float32 FMA in a fixed
 // order along k.  MODE 0: act[slot, j] = silu(x[token] . gate_e[j]) * (x[token] . up_e[j]), the input rows
-// gathered through slot_pair.  MODE 1: y[slot, j] = act[slot] . down_e[j].
+// gathered through slot_pair.  MODE 1: y[slot, j] = act[slot] . down_e[j].  MODE 2 (experts without a gate):
+// act[slot, j] = relu(x[token] . up_e[j])^2, the input rows gathered like MODE 0's, w0 the up matrices.
 struct MoeGemmArgs {
     const void* x;            // MODE 0: [rows, ldx] the layer's normed input; MODE 1: act [slots, ldx]
     const void* w0;           // MODE 0: gate [experts, J, K]; MODE 1: down [experts, J, K]
@@ -210,7 +211,7 @@ moe_gemm_simt_kernel(MoeGemmArgs a) {
     const int ts = threadIdx.x >> 4, tj = threadIdx.x & 15;  // ts: slot, tj: group of four outputs
     const int my_pair = a.slot_pair[slot0 + ts];
     // the row this thread fetches for the x tile: thread (r = tid >> 4, c = tid & 15) loads x[slot r][k0 + c]
-    const long long src_row = (MODE == 0) ? (my_pair >= 0 ? my_pair / a.top : -1) : (slot0 + ts);
+    const long long src_row = (MODE != 1) ? (my_pair >= 0 ? my_pair / a.top : -1) : (slot0 + ts);
     const T* w0 = (const T*)a.w0 + (size_t)e * a.J * a.K;
     const T* w1 = (MODE == 0) ? (const T*)a.w1 + (size_t)e * a.J * a.K : nullptr;
     float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -248,6 +249,9 @@ moe_gemm_simt_kernel(MoeGemmArgs a) {
         if (MODE == 0) {
             const float g = acc0[j];
             o[m] = from_f32<T>(my_pair >= 0 ? g / (1.f + expf(-g)) * acc1[j] : 0.f);
+        } else if (MODE == 2) {
+            const float r = fmaxf(acc0[j], 0.f);
+            o[m] = from_f32<T>(my_pair >= 0 ? r * r : 0.f);
         } else {
             o[m] = from_f32<T>(acc0[j]);
         }
@@ -269,6 +273,8 @@ extern "C" int braid_moe_gemm_simt(const void* x, const void* w0, const void* w1
     else if (dtype == BRAID_F32 && mode == 1) braid_launch(moe_gemm_simt_kernel<float, 1>, grid, dim3(256), 0, s, a);
     else if (dtype == BRAID_BF16 && mode == 0) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 0>, grid, dim3(256), 0, s, a);
     else if (dtype == BRAID_BF16 && mode == 1) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 1>, grid, dim3(256), 0, s, a);
+    else if (dtype == BRAID_F32 && mode == 2) braid_launch(moe_gemm_simt_kernel<float, 2>, grid, dim3(256), 0, s, a);
+    else if (dtype == BRAID_BF16 && mode == 2) braid_launch(moe_gemm_simt_kernel<__nv_bfloat16, 2>, grid, dim3(256), 0, s, a);
     else BRAID_REFUSE("moe_gemm: unknown dtype %d or mode %d", dtype, mode);
     BRAID_LAUNCH_CHECK();
 }
@@ -276,7 +282,8 @@ extern "C" int braid_moe_gemm_simt(const void* x, const void* w0, const void* w1
 // ------------------------------------------------------------------ the experts' products on the tensor cores
 // bfloat16, mma.sync with float32 accumulators (mma_tile.cuh).  One CTA a plan tile of BM slots (the plan's
 // tile is BM) and BN outputs.  MODE 0 multiplies the gathered rows with the expert's gate and up matrices at
-// once and stores silu(gate) * up; MODE 1 multiplies the activations with the down matrix.
+// once and stores silu(gate) * up; MODE 1 multiplies the activations with the down matrix; MODE 2 multiplies the
+// gathered rows with the expert's up matrix alone and stores relu(.)^2.
 template <int BM, int BN, int MODE>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(MoeGemmArgs a) {
@@ -300,7 +307,7 @@ moe_gemm_mma_kernel(MoeGemmArgs a) {
         const int r = (tid + i * 128) >> 2;
         a_rows[i] = nullptr;
         if (r < BM) {
-            if (MODE == 0) {
+            if (MODE != 1) {
                 const int pair = a.slot_pair[slot0 + r];
                 if (pair >= 0) a_rows[i] = x + (size_t)(pair / a.top) * a.ldx;
             } else {
@@ -333,6 +340,10 @@ moe_gemm_mma_kernel(MoeGemmArgs a) {
                     const float g0 = acc[0][mi][ni][half * 2], g1 = acc[0][mi][ni][half * 2 + 1];
                     v0 = live ? g0 / (1.f + expf(-g0)) * acc[NB - 1][mi][ni][half * 2] : 0.f;
                     v1 = live ? g1 / (1.f + expf(-g1)) * acc[NB - 1][mi][ni][half * 2 + 1] : 0.f;
+                } else if (MODE == 2) {
+                    const float r0 = fmaxf(acc[0][mi][ni][half * 2], 0.f), r1 = fmaxf(acc[0][mi][ni][half * 2 + 1], 0.f);
+                    v0 = live ? r0 * r0 : 0.f;
+                    v1 = live ? r1 * r1 : 0.f;
                 } else {
                     v0 = acc[0][mi][ni][half * 2];
                     v1 = acc[0][mi][ni][half * 2 + 1];
@@ -377,6 +388,8 @@ extern "C" int braid_moe_gemm_mma(const void* x, const void* w0, const void* w1,
     else if (tile == 64 && mode == 1) MOE_MMA(64, 128, 1);
     else if (tile == 16 && mode == 0) MOE_MMA(16, 64, 0);
     else if (tile == 16 && mode == 1) MOE_MMA(16, 64, 1);
+    else if (tile == 64 && mode == 2) MOE_MMA(64, 128, 2);
+    else if (tile == 16 && mode == 2) MOE_MMA(16, 64, 2);
     else BRAID_REFUSE("moe_gemm_mma: unknown mode %d", mode);
 #undef MOE_MMA
     BRAID_LAUNCH_CHECK();

@@ -132,11 +132,11 @@ extern "C" int braid_act_mul_gather(const void* gate, long long gate_stride, con
     BRAID_LAUNCH_CHECK();
 }
 
-// h[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w: an RMS norm (plain weight) of a branch's result, added to the float32
-// stream.  y float32 [rows, width]; one CTA a row; sums in float32, the same order every time.
+// h[r] += y[r] / sqrt(mean(y[r]^2) + eps) * (w + w_offset): an RMS norm of a branch's result (w_offset 0 for plain weights,
+// 1 for zero-centred weights), added to the float32 stream.  y float32 [rows, width]; one CTA a row; sums in float32, the same order every time.
 template <typename TW>
 __global__ void __launch_bounds__(256)
-rmsnorm_add_kernel(float* __restrict__ h, const float* __restrict__ y, const TW* __restrict__ w, int width, float eps) {
+rmsnorm_add_kernel(float* __restrict__ h, const float* __restrict__ y, const TW* __restrict__ w, int width, float eps, float w_offset) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
@@ -145,16 +145,16 @@ rmsnorm_add_kernel(float* __restrict__ h, const float* __restrict__ y, const TW*
     for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = y[base + c]; ss = fmaf(v, v, ss); }
     ss = block_sum(ss, red);
     const float r = 1.f / sqrtf(ss / (float)width + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) h[base + c] += y[base + c] * r * to_f32(w[c]);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) h[base + c] += y[base + c] * r * (to_f32(w[c]) + w_offset);
 }
 
 extern "C" int braid_rmsnorm_add(float* h, const float* y, const void* w, int w_dtype, int rows, int width, float eps,
-                                 void* stream) {
+                                 float w_offset, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (width <= 0) BRAID_REFUSE("rmsnorm_add: width=%d must be positive", width);
     cudaStream_t s = (cudaStream_t)stream;
-    if (w_dtype == BRAID_F32) braid_launch(rmsnorm_add_kernel<float>, dim3(rows), dim3(256), 0, s, h, y, (const float*)w, width, eps);
-    else if (w_dtype == BRAID_BF16) braid_launch(rmsnorm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, s, h, y, (const __nv_bfloat16*)w, width, eps);
+    if (w_dtype == BRAID_F32) braid_launch(rmsnorm_add_kernel<float>, dim3(rows), dim3(256), 0, s, h, y, (const float*)w, width, eps, w_offset);
+    else if (w_dtype == BRAID_BF16) braid_launch(rmsnorm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, s, h, y, (const __nv_bfloat16*)w, width, eps, w_offset);
     else BRAID_REFUSE("rmsnorm_add: unknown dtype code %d", w_dtype);
     BRAID_LAUNCH_CHECK();
 }

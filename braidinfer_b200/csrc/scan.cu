@@ -179,6 +179,10 @@ extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, lon
 //       z float32 [rows, heads * dk].
 //   DECAY_HEAD (state-space duality): dt = softplus(d_t[h] + dt_bias[h]), a_t = exp(-exp(A_log[h]) dt) for every
 //       channel, kappa = dt, skip = D[h]; d in the run's type [rows, heads] (row stride gate_stride).
+//   DECAY_GIVEN (a matrix memory whose gates were worked out before, braid_mlstm_gates): a_t = gate[t, h] for every
+//       channel and kappa_t = kappa[t, h], both float32 with row stride gate_stride; no skip.  With `v_cols` < dv the
+//       value columns from v_cols on read as 1: the state's column v_cols is then the sum of the decayed keys
+//       (a normaliser), and the output's column v_cols its product with the query.
 // q and k: [rows, groups, dk] in the run's type (head h reads group h / (heads / groups)); v: [rows, heads, dv].
 // out: float32 [rows, heads * dv].  Everything is float32 arithmetic on the ordinary pipes: the recurrence, its
 // decays and its state are not to be rounded to fewer bits.
@@ -203,6 +207,7 @@ extern "C" int braid_causal_conv(const void* x, long long x_stride, void* y, lon
 #define SCAN_MAX_DK 256
 #define DECAY_CHANNEL 0
 #define DECAY_HEAD 1
+#define DECAY_GIVEN 2
 
 struct ScanArgs {
     const void* q; long long q_stride;
@@ -221,6 +226,8 @@ struct ScanArgs {
     float* wbuf; float* dbuf;
     int pass, chunk, max_chunks;
     int gate_is_decay;           // DECAY_CHANNEL: `gate` holds the decays themselves (braid_scan_decay), not their logits
+    const float* kappa;          // DECAY_GIVEN: the factor on the key, [rows, heads] with row stride gate_stride
+    int v_cols;                  // columns a head that v really holds (row stride v_stride); the rest of dv read as 1
 };
 
 // sigmoid(z)^(1 / tau) through log sigmoid(z) = min(z, 0) - log1p(exp(-|z|)): no overflow, full precision near one
@@ -309,6 +316,7 @@ linear_scan_kernel(ScanArgs a) {
     // registers (as they came, in the run's type) and go to shared memory, converted, when the walk has left it.
     constexpr int NQ = TB * DKP / SCAN_THREADS, NV = TB * DVT / SCAN_THREADS;
     T pq[NQ], pk[NQ], pv[NV], pg = from_f32<T>(0.f);
+    float pgd = 0.f, pgk = 0.f;
     float pa[MODE == DECAY_CHANNEL ? NQ : 1];
     auto fetch = [&](int t0) {
         const int nt = min(TB, t_end - t0);
@@ -327,9 +335,15 @@ linear_scan_kernel(ScanArgs a) {
             const int idx = tid + u * SCAN_THREADS;
             const int t = idx / DVT, jj = idx - t * DVT;
             const size_t row = (size_t)(r0 + t0 + t);
-            pv[u] = (t < nt && dvt * DVT + jj < dv) ? ((const T*)a.v)[row * a.v_stride + (size_t)h * dv + dvt * DVT + jj] : from_f32<T>(0.f);
+            const int col = dvt * DVT + jj;
+            pv[u] = (t < nt && col < a.v_cols) ? ((const T*)a.v)[row * a.v_stride + (size_t)h * a.v_cols + col]
+                                              : from_f32<T>((t < nt && col < dv) ? 1.f : 0.f);
         }
         if (MODE == DECAY_HEAD && tid < nt) pg = ((const T*)a.gate)[(size_t)(r0 + t0 + tid) * a.gate_stride + h];
+        if (MODE == DECAY_GIVEN && tid < nt) {
+            pgd = ((const float*)a.gate)[(size_t)(r0 + t0 + tid) * a.gate_stride + h];
+            pgk = a.kappa[(size_t)(r0 + t0 + tid) * a.gate_stride + h];
+        }
     };
     fetch(t_begin);
     for (int t0 = t_begin; t0 < t_end; t0 += TB) {
@@ -357,6 +371,7 @@ linear_scan_kernel(ScanArgs a) {
             skap[tid] = dt;
             sah[tid] = expf(head_a * dt);
         }
+        if (MODE == DECAY_GIVEN && tid < nt) { skap[tid] = pgk; sah[tid] = pgd; }
         if (t0 + TB < t_end) fetch(t0 + TB);
         __syncthreads();
         for (int t = 0; t < nt; ++t) {
@@ -416,7 +431,7 @@ linear_scan_kernel(ScanArgs a) {
         }
     if (a.pass == 1 && dvt == 0) {                           // the product of the chunk's decays, once per head
         const size_t base = (size_t)(seq * a.max_chunks + c) * a.heads + h;
-        if (MODE == DECAY_HEAD) {
+        if (MODE != DECAY_CHANNEL) {
             if (tid == 0) a.dbuf[base] = hprod;
         } else if (cg == 0) {
 #pragma unroll
@@ -447,7 +462,7 @@ scan_carry_kernel(ScanArgs a) {
         const size_t base = (size_t)(seq * a.max_chunks + c);
         float* w = a.wbuf + base * per_seq + idx;
         const float u = *w;
-        const float d = MODE == DECAY_HEAD ? a.dbuf[base * a.heads + h] : a.dbuf[(base * a.heads + h) * a.dk + i];
+        const float d = MODE != DECAY_CHANNEL ? a.dbuf[base * a.heads + h] : a.dbuf[(base * a.heads + h) * a.dk + i];
         *w = S;                                             // the state that chunk c starts from
         S = fmaf(d, S, u);
     }
@@ -461,7 +476,7 @@ static int scan_rows(int dk) { return dk <= 128 ? 8 : 16; }
 extern "C" long long braid_linear_scan_work_floats(int n_seqs, int max_q_len, int chunk, int heads, int dk, int dv, int mode) {
     if (chunk <= 0 || max_q_len < 2 * chunk) return 0;
     const long long chunks = (max_q_len + chunk - 1) / chunk;
-    return (long long)n_seqs * chunks * heads * ((long long)dk * dv + (mode == DECAY_HEAD ? 1 : dk));
+    return (long long)n_seqs * chunks * heads * ((long long)dk * dv + (mode != DECAY_CHANNEL ? 1 : dk));
 }
 
 extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
@@ -470,12 +485,15 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
                                  long long state_stride, long long state_offset, const int* q_start, const int* q_len,
                                  const int* slot_ids, int dtype, int mode, int n_seqs, int heads, int groups, int dk, int dv,
                                  float q_scale, float inv_tau, int max_q_len, int chunk, float* work, long long work_floats,
-                                 int gate_is_decay, void* stream) {
+                                 int gate_is_decay, const float* kappa, int v_cols, void* stream) {
     if (n_seqs <= 0) return BRAID_OK;
     if (heads <= 0 || groups <= 0 || heads % groups) BRAID_REFUSE("linear_scan: %d heads do not divide into %d groups", heads, groups);
     if (dk <= 0 || dk > SCAN_MAX_DK || dv <= 0) BRAID_REFUSE("linear_scan: key size %d must be in (0, %d], value size %d positive", dk, SCAN_MAX_DK, dv);
     if (!state || (state_offset & 3) || (state_stride & 3)) BRAID_REFUSE("linear_scan: the state area must be given, in multiples of 4 bytes");
-    if (mode != DECAY_CHANNEL && mode != DECAY_HEAD) BRAID_REFUSE("linear_scan: unknown decay mode %d", mode);
+    if (mode != DECAY_CHANNEL && mode != DECAY_HEAD && mode != DECAY_GIVEN) BRAID_REFUSE("linear_scan: unknown decay mode %d", mode);
+    if (mode == DECAY_GIVEN && !kappa) BRAID_REFUSE("linear_scan: given decays come with the factors on the keys");
+    if (v_cols <= 0 || v_cols > dv) v_cols = dv;
+    if (mode != DECAY_GIVEN && v_cols != dv) BRAID_REFUSE("linear_scan: value columns that read as 1 need given decays");
     if (mode == DECAY_HEAD && !a_log) BRAID_REFUSE("linear_scan: a decay per head needs A_log");
     if (dtype != BRAID_F32 && dtype != BRAID_BF16) BRAID_REFUSE("linear_scan: unknown dtype code %d", dtype);
     const int rg = scan_rg(dk), rr = scan_rows(dk);
@@ -488,7 +506,7 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
     if (n_seqs > 65535 || (long long)n_dvt * max_chunks > 65535) BRAID_REFUSE("linear_scan: the step exceeds the grid limits");
     ScanArgs a{q, q_stride, k, k_stride, v, v_stride, gate, gate_stride, gate_bias, a_log, skip, out, out_stride,
                (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, groups, dk, dv, q_scale, inv_tau,
-               nullptr, nullptr, 0, chunk, max_chunks, gate_is_decay};
+               nullptr, nullptr, 0, chunk, max_chunks, gate_is_decay, kappa, v_cols};
     if (chunked) {
         a.wbuf = work;
         a.dbuf = work + (long long)n_seqs * max_chunks * heads * dk * dv;
@@ -506,9 +524,11 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
 #define SCAN_LAUNCH(GRID)                                                                                     \
     do {                                                                                                      \
         if (dtype == BRAID_F32 && mode == DECAY_CHANNEL) SCAN_LAUNCH_RG(float, DECAY_CHANNEL, GRID);          \
-        else if (dtype == BRAID_F32) SCAN_LAUNCH_RG(float, DECAY_HEAD, GRID);                                 \
+        else if (dtype == BRAID_F32 && mode == DECAY_HEAD) SCAN_LAUNCH_RG(float, DECAY_HEAD, GRID);           \
+        else if (dtype == BRAID_F32) SCAN_LAUNCH_RG(float, DECAY_GIVEN, GRID);                                \
         else if (mode == DECAY_CHANNEL) SCAN_LAUNCH_RG(__nv_bfloat16, DECAY_CHANNEL, GRID);                   \
-        else SCAN_LAUNCH_RG(__nv_bfloat16, DECAY_HEAD, GRID);                                                 \
+        else if (mode == DECAY_HEAD) SCAN_LAUNCH_RG(__nv_bfloat16, DECAY_HEAD, GRID);                         \
+        else SCAN_LAUNCH_RG(__nv_bfloat16, DECAY_GIVEN, GRID);                                                \
     } while (0)
     if (!chunked) {
         const dim3 grid(heads, n_seqs, n_dvt);
@@ -520,7 +540,7 @@ extern "C" int braid_linear_scan(const void* q, long long q_stride, const void* 
     SCAN_LAUNCH(grid);
     const long long per_seq = (long long)heads * dk * dv;
     const dim3 cgrid((unsigned)((per_seq + 255) / 256), n_seqs);
-    if (mode == DECAY_HEAD) braid_launch(scan_carry_kernel<DECAY_HEAD>, cgrid, dim3(256), 0, s, a);
+    if (mode != DECAY_CHANNEL) braid_launch(scan_carry_kernel<DECAY_HEAD>, cgrid, dim3(256), 0, s, a);
     else braid_launch(scan_carry_kernel<DECAY_CHANNEL>, cgrid, dim3(256), 0, s, a);
     a.pass = 3;
     SCAN_LAUNCH(grid);
@@ -630,5 +650,128 @@ extern "C" int braid_gated_norm(const float* y, const void* gate, long long gate
         braid_launch(gated_norm_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(128), 0, s, y, (const __nv_bfloat16*)gate, gate_stride,
                      (const __nv_bfloat16*)w, w_len, (__nv_bfloat16*)out, out_stride, token_seq, rows, width, group, gate_first, eps, out_scale);
     else BRAID_REFUSE("gated_norm: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ gates of a matrix memory (mLSTM)
+// Per sequence and head, token by token, with a running maximum m that the state carries (float32 [heads] at
+// state_offset; zero when a slot is taken, so m starts at 0):
+//   li = cap tanh((zi + bi) / cap)                      log input gate
+//   lf = log sigmoid(cap tanh((zf + bf) / cap))         log forget gate
+//   m_t = max(lf + m_(t-1), li);  decay_t = exp(lf + m_(t-1) - m_t);  kappa_t = exp(li - m_t);  floor_t = exp(-m_t)
+// z: float32 [rows, 2 heads] (the input gates' logits, then the forget gates'), biases [heads] each in the run's
+// type.  out: float32 [rows, 3 heads]: decays, kappas, floors.  One warp a (sequence, head): a lane a token for
+// the transcendental work; the chain over m is walked by every lane alike, so a token's m does not depend on where
+// the step began.
+template <typename T>
+__global__ void __launch_bounds__(32)
+mlstm_gates_kernel(const float* __restrict__ z, long long z_stride, const T* __restrict__ bi, const T* __restrict__ bf,
+                   float* __restrict__ out, uint8_t* __restrict__ state, long long state_stride, long long state_offset,
+                   const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ slot_ids,
+                   int heads, float cap) {
+    pdl_trigger();
+    const int h = blockIdx.x, seq = blockIdx.y, lane = threadIdx.x;
+    const float b_i = to_f32(bi[h]), b_f = to_f32(bf[h]);
+    pdl_wait();
+    const int n = q_len[seq], r0 = q_start[seq];
+    if (n <= 0) return;
+    float* mp = (float*)(state + (size_t)slot_ids[seq] * state_stride + state_offset) + h;
+    float m = *mp;
+    const float inv_cap = 1.f / cap;
+    for (int t0 = 0; t0 < n; t0 += 32) {
+        const int t = t0 + lane;
+        float li = 0.f, lf = 0.f;
+        if (t < n) {
+            const float* zr = z + (size_t)(r0 + t) * z_stride;
+            li = cap * tanhf((zr[h] + b_i) * inv_cap);
+            const float x = cap * tanhf((zr[heads + h] + b_f) * inv_cap);
+            lf = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+        }
+        const int nt = min(32, n - t0);
+        float m_prev = 0.f, m_mine = 0.f;
+        for (int l = 0; l < nt; ++l) {
+            const float f = __shfl_sync(0xffffffffu, lf, l), i = __shfl_sync(0xffffffffu, li, l);
+            const float mn = fmaxf(f + m, i);
+            if (l == lane) { m_prev = m; m_mine = mn; }
+            m = mn;
+        }
+        if (t < n) {
+            float* o = out + (size_t)(r0 + t) * (3 * heads);
+            o[h] = expf(lf + m_prev - m_mine);
+            o[heads + h] = expf(li - m_mine);
+            o[2 * heads + h] = expf(-m_mine);
+        }
+    }
+    if (lane == 0) *mp = m;
+}
+
+extern "C" int braid_mlstm_gates(const float* z, long long z_stride, const void* bi, const void* bf, int dtype, float* out,
+                                 void* state, long long state_stride, long long state_offset, const int* q_start,
+                                 const int* q_len, const int* slot_ids, int n_seqs, int heads, float cap, void* stream) {
+    if (n_seqs <= 0) return BRAID_OK;
+    if (heads <= 0 || n_seqs > 65535) BRAID_REFUSE("mlstm_gates: heads=%d must be positive and %d sequences fit a launch", heads, n_seqs);
+    if (!(cap > 0.f)) BRAID_REFUSE("mlstm_gates: the cap %g must be positive", (double)cap);
+    if (!state || (state_offset & 3) || (state_stride & 3)) BRAID_REFUSE("mlstm_gates: the state area must be given, in multiples of 4 bytes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(heads, n_seqs);
+    if (dtype == BRAID_F32)
+        braid_launch(mlstm_gates_kernel<float>, grid, dim3(32), 0, s, z, z_stride, (const float*)bi, (const float*)bf, out,
+                     (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, cap);
+    else if (dtype == BRAID_BF16)
+        braid_launch(mlstm_gates_kernel<__nv_bfloat16>, grid, dim3(32), 0, s, z, z_stride, (const __nv_bfloat16*)bi,
+                     (const __nv_bfloat16*)bf, out, (uint8_t*)state, state_stride, state_offset, q_start, q_len, slot_ids, heads, cap);
+    else BRAID_REFUSE("mlstm_gates: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// The memory's read-out: y [rows, heads * (dv + 1)] float32 holds, a head, S^T q in its first dv columns and n . q in
+// the last.  o = y[:dv] / (max(|n . q|, floor) + 1e-6), floor = floors[row, head] (row stride floor_stride);
+// out = o / sqrt(mean(o^2) + eps) * w[head * dv + c] * sigmoid(gate[row, head * dv + c]), in the run's type.
+// One warp a (row, head); float32 throughout.
+template <typename T>
+__global__ void __launch_bounds__(128)
+mlstm_out_kernel(const float* __restrict__ y, const float* __restrict__ floors, long long floor_stride,
+                 const T* __restrict__ gate, long long gate_stride, const T* __restrict__ w, T* __restrict__ out,
+                 long long out_stride, const int* __restrict__ token_seq, int rows, int heads, int dv, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + warp;
+    if (item >= (long long)rows * heads) return;
+    const int row = (int)(item / heads), h = (int)(item - (long long)row * heads);
+    T* orow = out + (size_t)row * out_stride + (size_t)h * dv;
+    if (token_seq[row] < 0) {
+        for (int c = lane; c < dv; c += 32) orow[c] = from_f32<T>(0.f);
+        return;
+    }
+    const float* yr = y + ((size_t)row * heads + h) * (dv + 1);
+    const float inv = 1.f / (fmaxf(fabsf(yr[dv]), floors[(size_t)row * floor_stride + h]) + 1e-6f);
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) { const float u = yr[c] * inv; ss = fmaf(u, u, ss); }
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)dv + eps);
+    const T* gr = gate + (size_t)row * gate_stride + (size_t)h * dv;
+    for (int c = lane; c < dv; c += 32) {
+        const float sg = 1.f / (1.f + expf(-to_f32(gr[c])));
+        orow[c] = from_f32<T>(yr[c] * inv * r * to_f32(w[(size_t)h * dv + c]) * sg);
+    }
+}
+
+extern "C" int braid_mlstm_out(const float* y, const float* floors, long long floor_stride, const void* gate,
+                               long long gate_stride, const void* w, void* out, long long out_stride, const int* token_seq,
+                               int dtype, int rows, int heads, int dv, float eps, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (heads <= 0 || dv <= 0) BRAID_REFUSE("mlstm_out: heads=%d and dv=%d must be positive", heads, dv);
+    const long long blocks = ((long long)rows * heads + 3) / 4;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("mlstm_out: %lld (row, head) pairs exceed one launch", (long long)rows * heads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32)
+        braid_launch(mlstm_out_kernel<float>, dim3((int)blocks), dim3(128), 0, s, y, floors, floor_stride, (const float*)gate,
+                     gate_stride, (const float*)w, (float*)out, out_stride, token_seq, rows, heads, dv, eps);
+    else if (dtype == BRAID_BF16)
+        braid_launch(mlstm_out_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(128), 0, s, y, floors, floor_stride,
+                     (const __nv_bfloat16*)gate, gate_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride,
+                     token_seq, rows, heads, dv, eps);
+    else BRAID_REFUSE("mlstm_out: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }

@@ -81,7 +81,10 @@ class DecoderModel:
         [wanted rows, vocab] (None when nothing is wanted).  `tap(i, h)`, if given, is shown
         the float32 residual stream [rows, width] after the embedding (i = 0) and after
         schedule entry i - 1 (sums that a part left deferred are completed first)."""
-        h = self.embedding.forward(ctx.token_ids, ctx.rows)
+        if self.embedding.uses_positions:
+            h = self.embedding.forward(ctx.token_ids, ctx.rows, positions=ctx.positions)
+        else:
+            h = self.embedding.forward(ctx.token_ids, ctx.rows)
         if tap is not None:
             tap(0, h)
         h0 = h.clone() if self._keep_h0 else None

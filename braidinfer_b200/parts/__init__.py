@@ -5,4 +5,4 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, LAYER_I
 from .spec import CacheRequest, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
 from .runtime import Runtime
 from . import (attention, block, embedding, feedforward, injection, latent_attention, linear_attention,  # noqa: F401
-               moe, norm, parallel, rope, ssm, token_input)                                       # (registration)
+               mlstm, moe, norm, parallel, rope, ssm, token_input)                                       # (registration)

@@ -16,6 +16,16 @@ Options that other designs use, each off unless named:
     sink            one more term exp(sink) in the softmax's denominator that has no value:
                     p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)); a row may so give weight to nothing
     out_mult        a constant factor on the mixer's result
+    sink_name       a learned sink score a head (a stored tensor of num_heads numbers) instead of the constant `sink`
+    head_gate       a gate a head on the result: head h's output is multiplied by sigmoid(Wg x)_h, Wg a stored
+                    [num_heads, hidden] tensor whose rows ride in the stacked product; the attention kernels apply it
+    unit_qk_eps     every query and key head is divided by its root mean square, sqrt(mean(x^2) + eps), no weight
+    q_temp          {"coef", "every"}: the query at position p is multiplied by
+                    1 + coef * ln(floor((p + 1) / every) + 1), a temperature that sharpens long contexts
+    value_dim       the size of a value head where it differs from head_dim
+The last three are for heads that are not rotated (position encoding "none"): one kernel norms, scales and
+stores.  Keys, values and queries are then padded with zeros to one head size that the attention kernels take
+(max(head_dim, value_dim), rounded up to 16), which changes no score and no result.
 """
 from __future__ import annotations
 
@@ -33,7 +43,10 @@ from .spec import CacheRequest, PartSpec, TensorSpec
 class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (int | None),
     position_encoding (PartSpec), and tensor names q_proj, k_proj, v_proj, o_proj; optional qk_norm
-    ({"eps", "q_name", "k_name"}), value_from_key (bool), scale, sink (a score), out_mult."""
+    ({"eps", "q_name", "k_name"}), value_from_key (bool), scale, sink (a score), out_mult, sink_name, head_gate,
+    unit_qk_eps, q_temp ({"coef", "every"}), value_dim."""
+
+    plain_output = True
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
@@ -48,14 +61,39 @@ class GQAAttention(Mixer):
         pe: PartSpec = p["position_encoding"]
         self.pe = POSITION_ENCODINGS.get(pe.kind)(pe.params, prefix, runtime)
         self.value_from_key = bool(p.get("value_from_key", False))
+        self.vd = int(p.get("value_dim") or self.hd)
+        self.unit_qk_eps = float(p["unit_qk_eps"]) if p.get("unit_qk_eps") is not None else None
+        qt = p.get("q_temp")
+        self.q_temp = (float(qt["coef"]), int(qt["every"])) if qt else None
+        if self.q_temp and self.q_temp[1] < 1:
+            raise ValueError(f"gqa_attention: q_temp.every must be at least 1, got {self.q_temp[1]}")
+        # heads that are normed without weights, scaled by position or of two sizes go through the kernel that
+        # pads them to one size
+        gated = p.get("head_gate") is not None
+        self.prep = (self.unit_qk_eps is not None or self.q_temp is not None or self.vd != self.hd
+                     or (gated and pe.kind == "none"))
+        if gated and not self.prep and not (p.get("qk_norm") is not None or self.value_from_key):
+            raise ValueError("gqa_attention: a gate a head rides in the stacked product, which the plain rotation kernels "
+                             "take without further columns; it goes with head norms or with heads that are not rotated")
+        self.hd_pad = -(-max(self.hd, self.vd) // 16) * 16 if self.prep else self.hd
+        if self.prep and (pe.kind != "none" or self.value_from_key or p.get("qk_norm") is not None):
+            raise ValueError("gqa_attention: unit norms, a query temperature and a value size of its own are for heads "
+                             "without rotation, weighted head norms or keys as values")
         names = [prefix + p.get("q_proj", "self_attn.q_proj.weight"), prefix + p.get("k_proj", "self_attn.k_proj.weight")]
         outs = [self.nqh * self.hd, self.nkh * self.hd]
         if not self.value_from_key:
             names.append(prefix + p.get("v_proj", "self_attn.v_proj.weight"))
-            outs.append(self.nkh * self.hd)
+            outs.append(self.nkh * self.vd)
+        self.gate_col = None
+        if p.get("head_gate") is not None:
+            self.gate_col = sum(outs)
+            names.append(prefix + p["head_gate"])
+            outs.append(self.nqh)
         self.qkv = Linear(runtime, names, outs, self.hidden)
         self.o = Linear(runtime, [prefix + p.get("o_proj", "self_attn.o_proj.weight")], [self.hidden],
-                        self.nqh * self.hd)
+                        self.nqh * self.vd)
+        self.sink_name = prefix + p["sink_name"] if p.get("sink_name") is not None else None
+        self.head_sinks = None
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.sink = float(p["sink"]) if p.get("sink") is not None else None
         self.out_mult = float(p.get("out_mult", 1.0))
@@ -74,6 +112,8 @@ class GQAAttention(Mixer):
         if self.qk_norm:
             d[self.qk_norm[1]] = TensorSpec((self.hd,), init="one_plus_normal")
             d[self.qk_norm[2]] = TensorSpec((self.hd,), init="one_plus_normal")
+        if self.sink_name:
+            d[self.sink_name] = TensorSpec((self.nqh,), std=1.0)
         return d
 
     def load(self, tensors) -> None:
@@ -86,10 +126,12 @@ class GQAAttention(Mixer):
         self.pe.load(tensors)
         if self.qk_norm:
             self.q_norm_w, self.k_norm_w = tensors[self.qk_norm[1]], tensors[self.qk_norm[2]]
+        if self.sink_name:
+            self.head_sinks = tensors[self.sink_name].float().contiguous()       # scores are float32 in every run
 
     def cache_request(self) -> Optional[CacheRequest]:
         kind = "window" if self.window else "full"
-        return CacheRequest(kind, self.nkh, self.hd, self.window)
+        return CacheRequest(kind, self.nkh, self.hd_pad, self.window)
 
     def takes_row_scale(self) -> bool:
         return self.qkv.takes_row_scale()
@@ -98,8 +140,11 @@ class GQAAttention(Mixer):
         if cache is None:
             raise RuntimeError("gqa_attention needs a cache view")
         rt = self.rt
-        fused = self.pe.accepts_deferred
+        fused = self.pe.accepts_deferred and not self.prep
         qkv = self.qkv.forward(x, defer_to=ctx if fused else None, in_scale=ctx.take_row_scale(x))
+        gate = qkv[:, self.gate_col:self.gate_col + self.nqh] if self.gate_col is not None else None
+        if self.prep:
+            return self._forward_padded(qkv, gate, residual, ctx, cache)
         if self.qk_norm or self.value_from_key:
             self.pe.norm_encode_and_store(qkv, self.nqh, self.nkh, ctx, cache, self.q_norm_w, self.k_norm_w,
                                           self.qk_norm[0] if self.qk_norm else 0.0, self.value_from_key)
@@ -107,10 +152,34 @@ class GQAAttention(Mixer):
             self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
         rows = x.shape[0]
         out = rt.empty(rows, self.nqh * self.hd)
-        self._attend(qkv, out, ctx, cache)
+        self._attend(qkv, out, ctx, cache, self.hd, gate)
+        return self._project(out, residual, ctx)
+
+    def _project(self, out, residual, ctx):
+        if residual is None:
+            return self.o.forward(out, out_dtype=torch.float32)
         return self.o.forward(out, residual=residual, defer_to=ctx)
 
-    def _attend(self, qkv, out, ctx, cache) -> None:
+    def _forward_padded(self, qkv, gate, residual, ctx, cache):
+        """Heads without rotation: norm, temperature and the padding to one head size in one kernel, attention over
+        the padded heads, then the value columns alone go on to the output product."""
+        K = self.rt.kernels
+        rows, D = qkv.shape[0], self.hd_pad
+        q = self.rt.empty(rows, self.nqh * D)
+        coef, every = self.q_temp if self.q_temp else (0.0, 0)
+        write = cache is not None and not cache.read_only
+        K.head_prep_kv(qkv, q, ctx.positions, ctx.token_seq, cache.page_table if write else None,
+                       cache.storage if write else None, self.nqh, self.nkh, self.hd, self.vd, D,
+                       self.unit_qk_eps is not None, self.unit_qk_eps or 0.0, coef, every)
+        out = self.rt.empty(rows, self.nqh * D)
+        self._attend(q, out, ctx, cache, D, gate)
+        if D != self.vd:
+            y = self.rt.empty(rows, self.nqh * self.vd)
+            K.head_gate(out, None, y, self.nqh, D, self.vd)
+            out = y
+        return self._project(out, residual, ctx)
+
+    def _attend(self, qkv, out, ctx, cache, hd, gate=None) -> None:
         """Pick the attention kernel for this step.  float32 runs, and runs that ask for
         the plain kernels, use the one-warp-per-query kernel for everything.  bfloat16
         runs use the tcgen05 kernel for prompts (head sizes 64 and 128; "mma" as the
@@ -118,17 +187,17 @@ class GQAAttention(Mixer):
         size), and the mma.sync kernel with the context sliced for steps of few tokens,
         so that a handful of sequences still fills the machine."""
         K = self.rt.kernels
-        plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(self.hd))
+        plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(hd))
         if plain:
             K.attn_simple(qkv, out, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
-                          self.nqh, self.nkh, self.hd, cache.page_size, self.window, self.scale, sink=self.sink,
-                          out_scale=self.out_mult)
+                          self.nqh, self.nkh, hd, cache.page_size, self.window, self.scale, sink=self.sink,
+                          head_sinks=self.head_sinks, head_gate=gate, out_scale=self.out_mult)
             return
         few = ctx.max_q_len <= 8
-        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(self.hd):
+        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(hd):
             K.attn_tc(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before,
-                      ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale, sink=self.sink,
-                      out_scale=self.out_mult)
+                      ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, hd, self.window, self.scale, sink=self.sink,
+                      head_sinks=self.head_sinks, head_gate=gate, out_scale=self.out_mult)
             return
         n_splits = 1
         if few:
@@ -137,7 +206,8 @@ class GQAAttention(Mixer):
             span = min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len
             tiles = max(1, -(-span // 32))
             # one wave of CTAs over the device, and at least four key tiles a slice
-            n_splits = max(1, min(K.attn_decode_slots(self.hd) // ctas, tiles // 4, 64))
+            n_splits = max(1, min(K.attn_decode_slots(hd) // ctas, tiles // 4, 64))
         K.attn_mma(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before, ctx.token_seq,
-                   ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale,
-                   n_splits=n_splits, few_tokens=few, sink=self.sink, out_scale=self.out_mult)
+                   ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, hd, self.window, self.scale,
+                   n_splits=n_splits, few_tokens=few, sink=self.sink, head_sinks=self.head_sinks, head_gate=gate,
+                   out_scale=self.out_mult)

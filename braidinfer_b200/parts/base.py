@@ -27,6 +27,10 @@ class Part:
     # says so here; every other part is handed tensors that are already complete.
     accepts_deferred = False
 
+    # A mixer or feed-forward that sets this true takes `residual=None` and then returns its result alone
+    # (float32) instead of residual + result: for blocks that norm a sublayer's result before they add it.
+    plain_output = False
+
     def takes_row_scale(self) -> bool:
         """A mixer or feed-forward that looks up `ctx.take_row_scale(x)` for its input and applies the
         scale it finds (see StepContext.row_scales) answers True; only then is it ever handed rows whose
@@ -97,6 +101,7 @@ class Mixer(Part):
         `cache` is this run's `LayerCache` view or None; `state` is a uint8
         tensor [slots, state_bytes] for this layer or None.  Rows are the
         step's tokens packed sequence after sequence, padded rows last.
+        A mixer with `plain_output` may be called with `residual=None` and then returns mix(x) alone, float32.
         """
         raise NotImplementedError
 
@@ -108,6 +113,10 @@ class FeedForward(Part):
 
 
 class Embedding(Part):
+    # An embedding that sets this true is called as forward(token_ids, rows, positions=...) with the rows'
+    # positions in their sequences (int32 on the device): a learned vector a position, say.
+    uses_positions = False
+
     def forward(self, token_ids: torch.Tensor, rows: int) -> torch.Tensor:
         """token_ids [rows] int32 on the device -> the residual stream [rows, width], float32."""
         raise NotImplementedError

@@ -2,7 +2,8 @@
 
 Embedding: h[t, :] = float(E[token_t, :]), no scale (reference:
 kernels/megakernel_ops.hip:1757-1768); a model may name a constant factor on the rows (`scale`) and a
-norm of the scaled rows (`norm`), whose output is then the stream.  A model may also cap its logits:
+norm of the scaled rows (`norm`), whose output is then the stream, and a learned vector a position that is added to
+a token's row, unscaled (`positions`: the stored table's name and its number of rows).  A model may also cap its logits:
 logits <- cap * tanh(logits / cap) (`softcap`).  Head: logits = W h in float32
 (kernels/megakernel_ops.hip:1783-1835); W is lm_head.weight, or the embedding table
 when the model ties them (crates/braidinfer-runtime/src/model/model_load.rs:388-398).
@@ -20,8 +21,9 @@ from .spec import TensorSpec
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """params: vocab_size, hidden_size, name; optional scale (a factor on the rows, default 1) and norm
-    (a PartSpec of a norm whose `forward` takes `in_place=True`, applied to the scaled rows)."""
+    """params: vocab_size, hidden_size, name; optional scale (a factor on the rows, default 1), norm
+    (a PartSpec of a norm whose `forward` takes `in_place=True`, applied to the scaled rows) and positions
+    ({"name", "max"}: a stored table [max, hidden_size]; row p is added to the token at position p of its sequence)."""
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
@@ -32,9 +34,18 @@ class TokenEmbedding(Embedding):
         norm = params.get("norm")
         self.norm = NORMS.get(norm.kind)(norm.params, prefix, runtime) if norm is not None else None
         self.weight: Optional[torch.Tensor] = None
+        pos = params.get("positions")
+        self.pos_name = prefix + pos["name"] if pos else None
+        self.max_positions = int(pos["max"]) if pos else 0
+        self.uses_positions = bool(pos)
+        self.pos_table: Optional[torch.Tensor] = None
+        if pos and self.norm is not None:
+            raise ValueError("token_embedding: a norm of the rows and a table of positions are not combined")
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         d = {self.name: TensorSpec((self.vocab, self.hidden))}
+        if self.pos_name:
+            d[self.pos_name] = TensorSpec((self.max_positions, self.hidden))
         if self.norm is not None:
             d.update(self.norm.tensor_specs())
         return d
@@ -43,10 +54,15 @@ class TokenEmbedding(Embedding):
         self.weight = tensors[self.name]
         if self.norm is not None:
             self.norm.load(tensors)
+        if self.pos_name:
+            self.pos_table = tensors[self.pos_name]
 
-    def forward(self, token_ids: torch.Tensor, rows: int) -> torch.Tensor:
+    def forward(self, token_ids: torch.Tensor, rows: int, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         h = torch.empty((rows, self.hidden), dtype=torch.float32, device=self.rt.device)
-        self.rt.kernels.embed(self.weight, token_ids, h, scale=self.scale)
+        if self.pos_table is not None and positions is None:
+            raise RuntimeError("token_embedding: this model adds a vector a position and needs the rows' positions")
+        self.rt.kernels.embed(self.weight, token_ids, h, scale=self.scale, pos_table=self.pos_table,
+                              positions=positions if self.pos_table is not None else None)
         if self.norm is not None:
             h = self.norm.forward(h, None, in_place=True)
         return h

@@ -3,10 +3,15 @@ model names another (`activation`: "gelu_tanh" is the tanh form of gelu, 0.5 z (
 (reference: crates/braidinfer-runtime/src/megakernel/compile_layers.rs:373-386;
 kernels/megakernel_ops.hip:1474-1545 gate/up with silu as x / (1 + exp(-x)),
 :1559-1602 down with the residual).  Gate and up are one stacked product; on the
-tensor-core path the activation is its epilogue."""
+tensor-core path the activation is its epilogue.
+
+"clamped_glu": down( g * sigmoid(alpha * g) * (u + 1) ) with g = min(gate x, limit) and u = clamp(up x, -limit, limit):
+a gated unit whose two branches are bounded before they meet, and whose linear branch is offset by one."""
 from __future__ import annotations
 
 from typing import Dict
+
+import torch
 
 from .base import FEED_FORWARDS, FeedForward
 from .linear import Linear
@@ -45,4 +50,41 @@ class SwiGLU(FeedForward):
     def forward(self, x, residual, ctx):
         act = self.gate_up.forward(x, swiglu=True, in_scale=ctx.take_row_scale(x) if ctx is not None else None,
                                    activation=self.activation)
+        return self.down.forward(act, residual=residual, defer_to=ctx)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """params: hidden_size, intermediate_size, limit, alpha (default 1.702), tensor names gate_proj, up_proj, down_proj."""
+
+    plain_output = True
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.limit = float(p["limit"])
+        self.alpha = float(p.get("alpha", 1.702))
+        if not self.limit > 0:
+            raise ValueError(f"clamped_glu: the limit must be positive, got {self.limit}")
+        self.gate_up = Linear(runtime, [prefix + p.get("gate_proj", "mlp.gate"), prefix + p.get("up_proj", "mlp.up")],
+                              [self.inter, self.inter], self.hidden)
+        self.down = Linear(runtime, [prefix + p.get("down_proj", "mlp.down")], [self.hidden], self.inter)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        d = dict(self.gate_up.tensor_specs())
+        d.update(self.down.tensor_specs())
+        return d
+
+    def load(self, tensors) -> None:
+        self.gate_up.load(tensors)
+        self.down.load(tensors)
+
+    def forward(self, x, residual, ctx):
+        gu = self.gate_up.forward(x)                           # [rows, gate | up]
+        act = self.rt.empty(x.shape[0], self.inter)
+        self.rt.kernels.glu_clamp(gu, act, self.limit, self.alpha)
+        if residual is None:
+            return self.down.forward(act, out_dtype=torch.float32)
         return self.down.forward(act, residual=residual, defer_to=ctx)

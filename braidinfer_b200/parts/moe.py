@@ -14,6 +14,11 @@ over the sorted rows tile by tile, and the weighted sum adds a token's choices i
 what a token gets does not depend on its neighbours in the batch.  Nothing is read back by the host, and
 launch sizes follow from the step's shape alone.  A constant factor on the output (`out_mult`) rides on
 the weights.
+
+Options for other designs: `gated: False` makes an expert Wdown act(Wup x) without a gate matrix, with
+`activation: "relu2"` (the square of relu) as its act.  Softmax over all experts followed by the division by the
+chosen scores' sum is the softmax over the chosen logits alone, so routers that are described that way need no
+mode of their own.
 """
 from __future__ import annotations
 
@@ -29,8 +34,11 @@ from .spec import TensorSpec
 @FEED_FORWARDS.register("moe")
 class MixtureOfExperts(FeedForward):
     """params: hidden_size, intermediate_size (of one expert), experts, top, groups (default 1), keep
-    (groups kept, default all), out_mult (default 1), and tensor names: router, and expert_gate, expert_up,
-    expert_down as patterns with `{e}` for the expert's number."""
+    (groups kept, default all), out_mult (default 1), gated (default True), activation ("silu" with a gate, "relu2"
+    without), and tensor names: router, and expert_gate, expert_up, expert_down as patterns with `{e}` for the
+    expert's number."""
+
+    plain_output = True
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
@@ -42,6 +50,11 @@ class MixtureOfExperts(FeedForward):
         self.groups = int(p.get("groups", 1))
         self.keep = int(p.get("keep", self.groups))
         self.out_mult = float(p.get("out_mult", 1.0))
+        self.gated = bool(p.get("gated", True))
+        self.activation = p.get("activation", "silu" if self.gated else "relu2")
+        if (self.gated, self.activation) not in ((True, "silu"), (False, "relu2")):
+            raise ValueError(f"moe: experts {'with' if self.gated else 'without'} a gate and activation "
+                             f"{self.activation!r} are not built (silu with a gate, relu2 without)")
         if self.experts % self.groups:
             raise ValueError(f"{self.experts} experts do not form {self.groups} equal groups")
         if not (1 <= self.keep <= self.groups):
@@ -57,14 +70,16 @@ class MixtureOfExperts(FeedForward):
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         d = dict(self.router.tensor_specs())
         for e in range(self.experts):
-            d[self.gate_names[e]] = TensorSpec((self.inter, self.hidden))
+            if self.gated:
+                d[self.gate_names[e]] = TensorSpec((self.inter, self.hidden))
             d[self.up_names[e]] = TensorSpec((self.inter, self.hidden))
             d[self.down_names[e]] = TensorSpec((self.hidden, self.inter))
         return d
 
     def load(self, tensors) -> None:
         self.router.load(tensors)
-        self.w_gate = torch.stack([tensors[n] for n in self.gate_names]).contiguous()     # [experts, inter, hidden]
+        if self.gated:
+            self.w_gate = torch.stack([tensors[n] for n in self.gate_names]).contiguous() # [experts, inter, hidden]
         self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()
         self.w_down = torch.stack([tensors[n] for n in self.down_names]).contiguous()     # [experts, hidden, inter]
 
@@ -85,6 +100,8 @@ class MixtureOfExperts(FeedForward):
         act = self.rt.empty(slots, self.inter)
         y = self.rt.empty(slots, self.hidden)
         self._experts(x, act, y, plan, tile)
+        if residual is None:
+            residual = torch.zeros((rows, self.hidden), dtype=torch.float32, device=x.device)
         K.moe_combine(residual, y, plan, wgt)
         return residual
 
@@ -92,9 +109,11 @@ class MixtureOfExperts(FeedForward):
         """bfloat16 rows that start on 16 bytes run on the tensor cores, everything else on the plain kernels."""
         K = self.rt.kernels
         tc = self.rt.gemm_backend == "auto"
-        if tc and K.moe_gemm_mma_eligible(x, self.w_gate, tile) and K.moe_gemm_mma_eligible(act, self.w_down, tile):
-            K.moe_gemm_mma(x, self.w_gate, self.w_up, act, plan, self.top, tile)
+        w0, w1 = (self.w_gate, self.w_up) if self.gated else (self.w_up, None)
+        relu2 = not self.gated
+        if tc and K.moe_gemm_mma_eligible(x, w0, tile) and K.moe_gemm_mma_eligible(act, self.w_down, tile):
+            K.moe_gemm_mma(x, w0, w1, act, plan, self.top, tile, relu2=relu2)
             K.moe_gemm_mma(act, self.w_down, None, y, plan, self.top, tile)
             return
-        K.moe_gemm_simt(x, self.w_gate, self.w_up, act, plan, self.top, tile)
+        K.moe_gemm_simt(x, w0, w1, act, plan, self.top, tile, relu2=relu2)
         K.moe_gemm_simt(act, self.w_down, None, y, plan, self.top, tile)

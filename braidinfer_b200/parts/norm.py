@@ -7,7 +7,10 @@ weight and a bias vector: no mean, no variance, nothing shared along a row (Zhu,
 RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, plain w
 (reference: kernels/megakernel_ops.hip:862-904; `1 + w` is another model family's rule,
 crates/braidinfer-runtime/src/config.rs:552).  Reads the float32 residual stream, writes
-the run's element type; the sum of squares and the scale are float32."""
+the run's element type; the sum of squares and the scale are float32.  With `offset` the stored weight w is
+zero-centred and applied as offset + w (offset 1: y = x * rsqrt(mean(x^2) + eps) * (1 + w)), added in float32.
+`add_into(y, h)` norms a branch's float32 result y and adds it to the float32 stream h in one kernel, for
+layers that norm what a sublayer returns instead of what it reads."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -21,7 +24,7 @@ from .spec import TensorSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """params: width, eps, name (tensor name under the prefix)."""
+    """params: width, eps, name (tensor name under the prefix), offset (added to the stored weight; default 0)."""
 
     accepts_deferred = True      # adds a deferred residual sum in the same kernel as the norm
 
@@ -30,10 +33,18 @@ class RMSNorm(Norm):
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.name = prefix + params["name"]
+        self.offset = float(params.get("offset", 0.0))
+        if self.offset:
+            self.accepts_deferred = False        # the kernels that add up partial sums apply plain weights
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.name: TensorSpec((self.width,), init="one_plus_normal")}
+        return {self.name: TensorSpec((self.width,), init="normal" if self.offset else "one_plus_normal")}
+
+    def add_into(self, y: torch.Tensor, h: torch.Tensor, ctx=None) -> torch.Tensor:
+        """h += norm(y), both float32 [rows, width]; returns h."""
+        self.rt.kernels.rmsnorm_add(h, y, self.weight, self.eps, w_offset=self.offset)
+        return h
 
     def load(self, tensors) -> None:
         self.weight = tensors[self.name]
@@ -42,6 +53,9 @@ class RMSNorm(Norm):
                 rows: Optional[int] = None, reader_takes_row_scale: bool = False) -> torch.Tensor:
         n = rows if rows is not None else x.shape[0]
         out = self.rt.empty(n, self.width)
+        if self.offset:
+            self.rt.kernels.rmsnorm(x, self.weight, out, self.eps, row_index=row_index, w_offset=self.offset)
+            return out
         d = ctx.take_deferred(x) if ctx is not None else None
         if (reader_takes_row_scale and self.rt.scaled_norm and ctx is not None and row_index is None and out.dtype == torch.bfloat16
                 and n <= ROW_SCALE_MAX_ROWS and self.width % 4 == 0 and self.rt.gemm_backend == "auto"):
