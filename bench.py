@@ -1117,6 +1117,274 @@ def loduzen_kernels(z, T, B, C, timed, frac):
     return res
 
 
+# ------------------------------------------------------------------ the Birepel decoder beside the Loduzen one
+def birepel_config(z):
+    """Attention and matrix-memory layers in turn at the sizes of `LODUZEN_SIZES`: the attention heads of the other
+    model's attention, the memory heads of its linear attention, its feed-forward (clamped here), and in the second
+    layer eight experts of which two serve a token, sized so that a token's products equal the dense unit's."""
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "q_temp": {"coef": 0.1, "every": 1024}}
+    mem = {"heads": z["lheads"], "dim": z["ldk"], "vdim": z["ldv"], "gate_cap": 15.0}
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": (3 * z["ff"] // 4) // 64 * 64}, "router": {"experts": 8, "top": 2}}
+    layers = []
+    for i in range(z["layers"]):
+        layers.append({"type": "attention", "mixer": att, "mlp": dense} if i % 2 == 0 else
+                      {"type": "mlstm", "mixer": mem, "mlp": moe if i == 1 else dense})
+    return {"architecture": "Birepel", "vocab": z["vocab"], "width": z["width"], "max_positions": 16384, "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
+def run_birepel(args):
+    """`--birepel`: prompt and decode throughput of the Birepel decoder at sizes like a real model's layers (random
+    weights, four layers), beside the Loduzen decoder of equal size (the closest model here: attention with a sink
+    beside recurrent layers with a matrix of state), and the new kernels one by one beside that model's like kernels
+    with their fractions of the measured peaks.  Prints one JSON line of its own; the default run and its line are
+    untouched."""
+    import torch
+    from braidinfer_b200.engine import Engine
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps=5, warm=2, graph=False):
+        for _ in range(warm):
+            fn()
+        run = fn
+        if graph:
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            run = gr.replay
+            run()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 1e3)
+        return statistics.median(ts)
+
+    def frac(seconds, flops, nbytes):
+        return max(flops / (pk["bf16_tflops"] * 1e12), nbytes / (pk["hbm_gbs"] * 1e9)) / seconds
+
+    T, B, C = args.prompt_len, args.batch, args.context
+    sizes = [n for n in LODUZEN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    out = {"metric": "birepel_beside_loduzen_decoder", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic, random weights",
+           "prompt_len": T, "decode_batch": B, "decode_context": C, "peaks": pk, "l2": "flushed between timed calls", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name in sizes:
+            z = LODUZEN_SIZES[name]
+            row = {}
+            for label, cfg in (("birepel", birepel_config(z)), ("loduzen", loduzen_config(z))):
+                eng = Engine.from_random(cfg, 1, dtype="bfloat16", on_device=True, max_tokens=max(B * (C + 192), T + 64),
+                                         max_slots=B, verbose=False)
+                g = torch.Generator().manual_seed(0)
+                prompt = torch.randint(0, z["vocab"], (T,), generator=g).tolist()
+
+                def prefill():
+                    s = eng.open()
+                    eng.step([(s, prompt)], want="last")
+                    eng.close(s)
+                tp = timed(prefill, reps=3, warm=2)
+                prompts = [torch.randint(0, z["vocab"], (C,), generator=g).tolist() for _ in range(B)]
+                secs, ctx0, launches = device_timed_decode(eng, eng.kernels, prompts, args.steps, max(args.warmup, 3))
+                eng.check()
+                row[label] = {"prefill_tokens_per_s": round(T / tp), "prefill_ms": round(tp * 1e3, 3),
+                              "decode_tokens_per_s": round(B * args.steps / secs), "decode_ms_per_step": round(secs / args.steps * 1e3, 4),
+                              "weight_gb": round(eng.weight_bytes / 1e9, 3), "state_mb_per_sequence": round(sum(
+                                  s.shape[1] for s in eng.cache.state if s is not None) / 1e6, 3),
+                              "launches_per_decode_step": launches // args.steps}
+                del eng
+                torch.cuda.empty_cache()
+            row["kernels"] = birepel_kernels(z, T, B, C, timed, frac)
+            out["sizes"][name] = row
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
+def birepel_kernels(z, T, B, C, timed, frac):
+    """The new kernels alone, each beside the Loduzen decoder's like kernel: seconds, and the fraction of the measured
+    peak that its algorithmic FLOPs or bytes (whichever bounds it) reach.  The recurrences run on the ordinary float32
+    pipes: their `frac` is of the copy bandwidth (the bytes they must move), and `tflops` says what they compute."""
+    import torch
+    from types import SimpleNamespace
+    from braidinfer_b200.cache import PAGE_SIZE
+    from braidinfer_b200.csrc.api import get_kernels
+    K = get_kernels(verbose=False)
+    dev, bf = "cuda", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    H, nkh, hd, Wd, win = z["heads"], z["kv"], z["dim"], z["width"], z["window"]
+    hbm = peaks()["hbm_gbs"]
+    res = {}
+
+    def paged(n_seqs, length):
+        blocks = -(-length // PAGE_SIZE)
+        cache = torch.randn(n_seqs * blocks, 2, nkh, PAGE_SIZE, hd, device=dev, dtype=bf) * 0.5
+        table = torch.arange(n_seqs * blocks, dtype=torch.int32, device=dev).view(n_seqs, blocks)
+        return cache, table
+
+    def steps_of(n_seqs, each, before):
+        rows = n_seqs * each
+        return SimpleNamespace(rows=rows, n_tokens=rows, n_seqs=n_seqs, q_start=i32([i * each for i in range(n_seqs)]),
+                               q_len=i32([each] * n_seqs), kv_before=i32([before] * n_seqs), slot_ids=i32(list(range(n_seqs))), max_q_len=each,
+                               token_seq=torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each),
+                               positions=(torch.arange(each, dtype=torch.int32, device=dev) + before).repeat(n_seqs))
+
+    st, sd = steps_of(1, T, 0), steps_of(B, 1, C - 1)
+    sinks = torch.randn(H, device=dev)
+
+    # ---- attention over a prompt of T tokens: a sink and a gate a head (no window) beside one sink for all (windowed)
+    cache, table = paged(1, T)
+    q = torch.randn(T, H * hd + 64, device=dev, dtype=bf) * 0.3
+    gate = q[:, H * hd:H * hd + H]
+    o = torch.empty(T, H * hd, device=dev, dtype=bf)
+    fl_full = 2 * 2 * H * hd * (T * (T + 1) // 2)
+    fl_win = 2 * 2 * H * hd * sum(min(p + 1, win) for p in range(T))
+    row = {}
+    for label, kw, w, fl in (("birepel", dict(head_sinks=sinks, head_gate=gate), None, fl_full),
+                             ("loduzen", dict(sink=0.0, out_scale=1.2), win, fl_win)):
+        t = timed(lambda: K.attn_mma(q, o, cache, table, st.q_start, st.q_len, st.kv_before, st.token_seq, 1, T, H, nkh, hd, w,
+                                     hd ** -0.5, **kw), graph=True)
+        row.update({label + "_mma_ms": round(t * 1e3, 3), label + "_mma_frac": round(frac(t, fl, 0), 3)})
+        if K.attn_tc_supports(hd):
+            t = timed(lambda: K.attn_tc(q, o, cache, table, st.q_start, st.q_len, st.kv_before, 1, T, H, nkh, hd, w, hd ** -0.5, **kw),
+                      graph=True)
+            row.update({label + "_tcgen05_ms": round(t * 1e3, 3), label + "_tcgen05_frac": round(frac(t, fl, 0), 3)})
+    res["prompt_attention"] = row
+
+    # ---- attention of B decoded tokens over a context of C (Loduzen's window caps what it reads)
+    cache, table = paged(B, C)
+    qd = torch.randn(B, H * hd + 64, device=dev, dtype=bf) * 0.3
+    gd = qd[:, H * hd:H * hd + H]
+    od = torch.empty(B, H * hd, device=dev, dtype=bf)
+    g = H // nkh
+    row = {}
+    for label, kw, w in (("birepel", dict(head_sinks=sinks, head_gate=gd), None), ("loduzen", dict(sink=0.0), win)):
+        span = min(C, w) if w else C
+        sp = max(1, min(K.attn_decode_slots(hd) // (B * nkh * -(-g // 16)), (span // 32) // 4, 64))
+        by = B * span * 2 * nkh * hd * 2
+        t = timed(lambda: K.attn_mma(qd, od, cache, table, sd.q_start, sd.q_len, sd.kv_before, sd.token_seq, B, 1, H, nkh, hd, w,
+                                     hd ** -0.5, n_splits=sp, few_tokens=True, **kw), reps=9, graph=True)
+        row.update({label + "_ms": round(t * 1e3, 4), label + "_frac": round(frac(t, 0, by), 3), label + "_slices": sp})
+    res["decode_attention"] = row
+
+    # ---- unit heads + temperature + cache write (one kernel) beside Loduzen's norm of heads + rotation + cache write
+    inv = torch.rand(hd // 4, device=dev)
+    wn = torch.ones(hd, device=dev, dtype=bf)
+    for what, stp, n_seqs, length in (("prompt_prep", st, 1, T), ("decode_prep", sd, B, C)):
+        cache, table = paged(n_seqs, length)
+        rows = stp.rows
+        src = torch.randn(rows, (H + 2 * nkh) * hd + 64, device=dev, dtype=bf)
+        qo = torch.empty(rows, H * hd, device=dev, dtype=bf)
+        qk = torch.randn(rows, (H + nkh) * hd, device=dev, dtype=bf)
+        t1 = timed(lambda: K.head_prep_kv(src, qo, stp.positions, stp.token_seq, table, cache, H, nkh, hd, hd, hd, True, 1e-6, 0.1, 1024),
+                   reps=9, graph=True)
+        t2 = timed(lambda: K.head_norm_rope_kv(qk, wn, wn, inv, stp.positions, stp.token_seq, table, cache, H, nkh, hd, hd // 2, True,
+                                               True, PAGE_SIZE, 1e-6, 1.1), reps=9, graph=True)
+        by1 = rows * hd * 2 * (2 * H + 4 * nkh)                  # heads read, queries and two cache planes written
+        by2 = rows * hd * 2 * (2 * (H + nkh) + 2 * nkh)
+        res[what] = {"birepel_ms": round(t1 * 1e3, 4), "birepel_frac": round(frac(t1, 0, by1), 3),
+                     "loduzen_ms": round(t2 * 1e3, 4), "loduzen_frac": round(frac(t2, 0, by2), 3)}
+
+    # ---- the recurrences: the matrix memory (decays and key factors given, a normaliser as one more column) beside
+    # gated linear attention (a decay per channel) at the same heads and sizes; with them the gates and the read-outs
+    heads, dk, dv = z["lheads"], z["ldk"], z["ldv"]
+    for what, stp in (("prompt", st), ("decode", sd)):
+        rows, n_seqs = stp.rows, stp.n_seqs
+        qq = torch.randn(rows, heads * dk, device=dev, dtype=bf) * 0.1
+        kk = torch.randn(rows, heads * dk, device=dev, dtype=bf) * 0.1
+        vv = torch.randn(rows, heads * dv, device=dev, dtype=bf)
+        bias = torch.zeros(heads * dk, device=dev, dtype=bf)
+        # the memory
+        m_off = heads * dk * (dv + 1) * 4
+        state = torch.zeros(n_seqs, m_off + heads * 4, dtype=torch.uint8, device=dev)
+        zz = torch.randn(rows, 2 * heads, device=dev) * 2
+        zz[:, heads:] += 4.0
+        gates = torch.empty(rows, 3 * heads, device=dev)
+        bi = torch.zeros(heads, device=dev, dtype=bf)
+        t = timed(lambda: K.mlstm_gates(zz, bi, bi, gates, state, m_off, stp, heads, 15.0), reps=9, graph=True)
+        res[f"{what}_memory_gates"] = {"ms": round(t * 1e3, 4), "mb": round(rows * heads * 20 / 1e6, 3),
+                                       "frac": round(frac(t, 0, rows * heads * 20), 4)}
+        K.mlstm_gates(zz, bi, bi, gates, state, m_off, stp, heads, 15.0)
+        oo = torch.empty(rows, heads * (dv + 1), device=dev)
+        t = timed(lambda: K.linear_scan(qq, kk, vv, gates[:, :heads], bi, oo, state, 0, stp, heads, heads, dk, dv + 1, "given",
+                                        q_scale=dk ** -0.5, kappa=gates[:, heads:2 * heads], v_cols=dv), reps=5, graph=True)
+        by = rows * (2 * heads * dk * 2 + heads * dv * 2 + heads * (dv + 1) * 4 + heads * 8) + 2 * n_seqs * heads * dk * (dv + 1) * 4
+        fl = 4 * rows * heads * dk * (dv + 1)
+        res[f"{what}_memory_scan"] = {"ms": round(t * 1e3, 4), "frac_of_bandwidth": round(by / (t * 1e9) / hbm, 3),
+                                      "tflops_fp32": round(fl / t / 1e12, 2), "mb": round(by / 1e6, 2)}
+        # Loduzen's gated linear attention
+        state2 = torch.zeros(n_seqs, heads * dk * dv * 4, dtype=torch.uint8, device=dev)
+        gate = torch.rand(rows, heads * dk, device=dev) * 0.1 + 0.9
+        o2 = torch.empty(rows, heads * dv, device=dev)
+        t = timed(lambda: K.linear_scan(qq, kk, vv, gate, bias, o2, state2, 0, stp, heads, heads, dk, dv, "channel",
+                                        q_scale=dk ** -0.5, inv_tau=1 / 8, gate_is_decay=rows > 64), reps=5, graph=True)
+        by = rows * (2 * heads * dk * 2 + heads * dv * 2 + heads * dv * 4 + heads * dk * 4) + 2 * n_seqs * heads * dk * dv * 4
+        fl = 4 * rows * heads * dk * dv
+        res[f"{what}_memory_scan"].update(loduzen_ms=round(t * 1e3, 4), loduzen_frac_of_bandwidth=round(by / (t * 1e9) / hbm, 3),
+                                          loduzen_tflops_fp32=round(fl / t / 1e12, 2))
+        # the read-outs: floor, unit norm a head, weight and gate beside Loduzen's gated norm
+        inner = heads * dv
+        gt = torch.randn(rows, inner, device=dev, dtype=bf)
+        wv = torch.ones(inner, device=dev, dtype=bf)
+        ob = torch.empty(rows, inner, device=dev, dtype=bf)
+        t1 = timed(lambda: K.mlstm_out(oo, gates[:, 2 * heads:], gt, wv, ob, stp.token_seq, heads, dv, 1e-6), reps=9, graph=True)
+        yy = torch.randn(rows, inner, device=dev)
+        t2 = timed(lambda: K.gated_norm(yy, gt, wv, ob, stp.token_seq, dv, True, 1e-6), reps=9, graph=True)
+        res[f"{what}_memory_read_out"] = {"birepel_ms": round(t1 * 1e3, 4), "birepel_frac": round(frac(t1, 0, rows * (inner * 8 + heads * 8)), 3),
+                                          "loduzen_ms": round(t2 * 1e3, 4), "loduzen_frac": round(frac(t2, 0, rows * inner * 8), 3)}
+        # the clamped gated unit beside the plain one
+        I = z["ff"]
+        gu = torch.randn(rows, 2 * I, device=dev, dtype=bf)
+        ao = torch.empty(rows, I, device=dev, dtype=bf)
+        t1 = timed(lambda: K.glu_clamp(gu, ao, 7.0, 1.702), reps=9, graph=True)
+        t2 = timed(lambda: K.silu_mul(gu, ao), reps=9, graph=True)
+        res[f"{what}_gated_unit"] = {"birepel_ms": round(t1 * 1e3, 4), "birepel_frac": round(frac(t1, 0, rows * I * 6), 3),
+                                     "loduzen_ms": round(t2 * 1e3, 4), "loduzen_frac": round(frac(t2, 0, rows * I * 6), 3)}
+        # the norm of what a sublayer returned, added to the stream (zero-centred weight) beside Loduzen's norm and sum
+        hres, ysub = torch.zeros(rows, Wd, device=dev), torch.randn(rows, Wd, device=dev)
+        w1 = torch.zeros(Wd, device=dev, dtype=bf)
+        t1 = timed(lambda: K.rmsnorm_add(hres, ysub, w1, 1e-6, w_offset=1.0), reps=9, graph=True)
+        t2 = timed(lambda: K.rmsnorm_add(hres, ysub, w1, 1e-6), reps=9, graph=True)
+        res[f"{what}_norm_add"] = {"birepel_ms": round(t1 * 1e3, 4), "birepel_frac": round(frac(t1, 0, rows * Wd * 12), 3),
+                                   "loduzen_ms": round(t2 * 1e3, 4), "loduzen_frac": round(frac(t2, 0, rows * Wd * 12), 3)}
+        # embedding with a learned position beside the embedding alone
+        tab = torch.randn(z["vocab"], Wd, device=dev, dtype=bf)
+        ptab = torch.randn(max(T, C) + 8, Wd, device=dev, dtype=bf)
+        ids = torch.randint(0, z["vocab"], (rows,), device=dev, dtype=torch.int32)
+        eo = torch.empty(rows, Wd, device=dev)
+        t1 = timed(lambda: K.embed(tab, ids, eo, 1.0, pos_table=ptab, positions=stp.positions), reps=9, graph=True)
+        t2 = timed(lambda: K.embed(tab, ids, eo, 1.0), reps=9, graph=True)
+        res[f"{what}_embedding"] = {"birepel_ms": round(t1 * 1e3, 4), "birepel_frac": round(frac(t1, 0, rows * Wd * 8), 3),
+                                    "loduzen_ms": round(t2 * 1e3, 4), "loduzen_frac": round(frac(t2, 0, rows * Wd * 6), 3)}
+        # experts without gates (squared relu) beside gated experts on the same plan: the first product of both
+        E, top, J = 8, 2, (3 * z["ff"] // 4) // 64 * 64
+        x = torch.randn(rows, Wd, device=dev, dtype=bf) * 0.1
+        wu = torch.randn(E, J, Wd, device=dev, dtype=bf) * 0.02
+        wg = torch.randn(E, J, Wd, device=dev, dtype=bf) * 0.02
+        lg = torch.randn(rows, E, device=dev)
+        idx = torch.empty(rows, top, dtype=torch.int32, device=dev)
+        wgt = torch.empty(rows, top, device=dev)
+        K.moe_route(lg, idx, wgt, 1, 1)
+        tile = 16 if rows * top <= 16 * E else 64
+        plan = K.moe_plan(idx, stp.token_seq, E, tile)
+        act = torch.empty(plan[4] * tile, J, device=dev, dtype=bf)
+        t1 = timed(lambda: K.moe_gemm_mma(x, wu, None, act, plan, top, tile, relu2=True), reps=5, graph=True)
+        t2 = timed(lambda: K.moe_gemm_mma(x, wg, wu, act, plan, top, tile), reps=5, graph=True)
+        used = min(E, rows * top)
+        res[f"{what}_experts_first_product"] = {
+            "birepel_ms": round(t1 * 1e3, 4), "birepel_frac": round(frac(t1, 2 * rows * top * J * Wd, used * J * Wd * 2), 3),
+            "gated_ms": round(t2 * 1e3, 4), "gated_frac": round(frac(t2, 4 * rows * top * J * Wd, 2 * used * J * Wd * 2), 3)}
+    K.check_device_errors()
+    return res
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
@@ -1155,7 +1423,10 @@ def main() -> int:
     ap.add_argument("--loduzen", action="store_true",
                     help="the Loduzen decoder (attention beside linear attention, state-space layers) beside the dense "
                          "decoder of equal size, and its kernels one by one; prints its own line (see run_loduzen)")
-    ap.add_argument("--sizes", default="", help="with --bidinex / --loduzen: names of the sizes, with commas (default: all)")
+    ap.add_argument("--birepel", action="store_true",
+                    help="another measurement: the Birepel decoder at sizes like a real model's layers beside the Loduzen "
+                         "decoder of equal size, and its kernels one by one; prints its own line (see run_birepel)")
+    ap.add_argument("--sizes", default="", help="with --bidinex / --loduzen / --birepel: names of the sizes, with commas (default: all)")
     ap.add_argument("--prompt-len", type=int, default=2048, help="with --bidinex: tokens of the timed prompt")
     ap.add_argument("--context", type=int, default=2048, help="with --bidinex: context of the timed decode steps")
     args = ap.parse_args()
@@ -1168,6 +1439,8 @@ def main() -> int:
         return run_bidinex(args)
     if args.loduzen:
         return run_loduzen(args)
+    if args.birepel:
+        return run_birepel(args)
     if args.sweep:
         return run_sweep(args)
     if args.prompt_timeline:

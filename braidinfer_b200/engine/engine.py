@@ -7,6 +7,7 @@ this one object.
 """
 from __future__ import annotations
 
+import gc
 import os
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple, Union
 
@@ -284,17 +285,26 @@ class Engine:
         graph = torch.cuda.CUDAGraph()
         stream = self._capture_stream
         stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
-            graph.capture_begin(self._graph_pool)
-            try:
-                static_logits = self.model.forward(ctx, self.cache)
-            except BaseException:
+        # The collector stays off while the stream records: were it to free another engine's graphs now (objects in
+        # a cycle that nothing names any more), their release is a call the driver refuses during a capture, and
+        # the capture would be lost.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.stream(stream):
+                graph.capture_begin(self._graph_pool)
                 try:
-                    graph.capture_end()              # leave capture mode before the error travels on
-                except Exception:
-                    pass
-                raise
-            graph.capture_end()
+                    static_logits = self.model.forward(ctx, self.cache)
+                except BaseException:
+                    try:
+                        graph.capture_end()              # leave capture mode before the error travels on
+                    except Exception:
+                        pass
+                    raise
+                graph.capture_end()
+        finally:
+            if collecting:
+                gc.enable()
         torch.cuda.current_stream().wait_stream(stream)
         return graph, static_logits
 

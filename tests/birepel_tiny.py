@@ -80,31 +80,57 @@ BR_CONFIGS = {"A": BR_A, "B": BR_B, "C": BR_C, "D": BR_D}
 BR_SEEDS = {"A": 5, "B": 19, "C": 23, "D": 43}
 
 # factors on the drawn tensors, by the end of their names
-GAINS = {"embed": 40.0, "pos": 15.0, ".mix.q": 10.0, ".mix.k": 10.0, ".mix.v": 10.0, ".mix.g": 20.0, ".mix.o": 6.0,
-         ".mix.i": 30.0, ".mix.f": 30.0, ".norm1": 10.0, ".norm2": 10.0, "final.norm": 10.0, ".mlp.gate": 8.0, ".mlp.up": 8.0,
+GAINS = {"embed": 40.0, "pos": 15.0, ".mix.q": 10.0, ".mix.k": 10.0, ".mix.v": 10.0, ".mix.g": 20.0, ".mix.o": 6.0, ".mix.sink": 3.0,
+         ".mix.i": 30.0, ".mix.f": 2.0, ".norm1": 10.0, ".norm2": 10.0, "final.norm": 10.0, ".mlp.gate": 8.0, ".mlp.up": 8.0,
          ".mlp.down": 8.0, ".mlp.router": 40.0, ".up": 10.0, ".down": 8.0}
 
 
-def shape_weights(tensors: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+def shape_weights(tensors: Dict[str, torch.Tensor], cfg: Dict = None, steady: bool = False, gains: Dict = None) -> Dict[str, torch.Tensor]:
+    """The drawn tensors times their gains.  `steady`: the routers' choices rest on no close call, whatever the
+    precision of the run.  The last columns of the stream, one an expert, are set apart: the table of positions and
+    every norm on a sublayer's output write nothing there, so they hold what the token's embedding put there, a
+    quarter times a permutation of 0 .. experts - 1 drawn for the token, and the router's row e reads column e of
+    them alone, times 8.  Its logits are then exact multiples of 2 in any run, no two of a token equal, while the
+    softmax over the chosen ones still mixes them (0.88 to 0.12 with two)."""
     out = {}
+    table = dict(GAINS, **(gains or {}))
     for n, t in tensors.items():
-        f = next((v for k, v in GAINS.items() if n.endswith(k)), 1.0)
+        f = next((v for k, v in table.items() if n.endswith(k)), 1.0)
         x = t.float() * f
         if n.endswith(".f.b"):
-            x = x + 4.0                    # forget gates near one: a memory keeps hundreds of tokens
+            x = x + 5.0                    # forget gates near one: a memory keeps hundreds of tokens
         out[n] = x.to(t.dtype)
+    if steady:
+        most = max([L["mlp"]["router"]["experts"] for L in cfg["layers"] if L.get("mlp") and L["mlp"]["kind"] == "moe"] or [0])
+        width = cfg["width"]
+        g = torch.Generator().manual_seed(width + most)
+        for n, t in out.items():
+            x = t.float()
+            if n == "pos":
+                x[:, width - most:] = 0.0
+            elif n == "embed":
+                for tok in range(x.shape[0]):
+                    x[tok, width - most:] = 0.25 * torch.randperm(most, generator=g).float()
+            elif n.endswith(".norm1") or n.endswith(".norm2"):
+                x[width - most:] = -1.0
+            elif n.endswith(".mlp.router"):
+                x.zero_()
+                for e in range(x.shape[0]):
+                    x[e, width - most + e] = 8.0
+            out[n] = x.to(t.dtype)
     return out
 
 
-def make_birepel_folder(tmp_path, name: str, cfg: Dict = None, seed: int = None) -> str:
-    """Write a model folder for configuration `name` (or `cfg`) with shaped random weights."""
+def make_birepel_folder(tmp_path, name: str, cfg: Dict = None, seed: int = None, steady: bool = False, gains: Dict = None) -> str:
+    """Write a model folder for configuration `name` (or `cfg`) with shaped random weights (`gains` replaces entries
+    of `GAINS`)."""
     from braidinfer_b200.weights import open_model_folder, save_file, write_random_model
     cfg = dict(cfg if cfg is not None else BR_CONFIGS[name])
     seed = BR_SEEDS.get(name, 1) if seed is None else seed
-    folder = os.path.join(str(tmp_path), f"birepel_{name}")
+    folder = os.path.join(str(tmp_path), f"birepel_{name}" + ("_steady" if steady else ""))
     write_random_model(cfg, folder, seed)
     tensors = {n: f.tensor(k).clone() for n, (f, k) in open_model_folder(folder).items()}
-    save_file(shape_weights(tensors), os.path.join(folder, "model.safetensors"))
+    save_file(shape_weights(tensors, cfg, steady, gains), os.path.join(folder, "model.safetensors"))
     return folder
 
 

@@ -77,8 +77,34 @@ def capped(z, cap):
     return cap * torch.tanh(z / cap)
 
 
+def memory_walk(q, k, v, li, lf, S=None, n=None, mx=None):
+    """One head's matrix memory along T tokens: q, k [T, dk] (q already scaled), v [T, dv], li and lf [T] the logarithms
+    of the input and forget gates.  Returns (o [T, dv], S [dk, dv], n [dk], m): the read-outs and the state after the
+    last token, held in units of exp(m).  The state starts at zero and m at 0 unless given."""
+    T, dk, dv = q.shape[0], q.shape[1], v.shape[1]
+    S = torch.zeros(dk, dv, dtype=D) if S is None else S.clone()
+    n = torch.zeros(dk, dtype=D) if n is None else n.clone()
+    mx = torch.zeros((), dtype=D) if mx is None else mx.clone()
+    out = torch.zeros(T, dv, dtype=D)
+    for t in range(T):
+        m_new = torch.maximum(lf[t] + mx, li[t])
+        keep, take = torch.exp(lf[t] + mx - m_new), torch.exp(li[t] - m_new)
+        S = keep * S + take * torch.outer(k[t], v[t])
+        n = keep * n + take * k[t]
+        mx = m_new
+        den = torch.maximum((n @ q[t]).abs(), torch.exp(-mx)) + 1e-6
+        out[t] = (S.T @ q[t]) / den
+    return out, S, n, mx
+
+
+FIRST_ANGLES = None        # a list, while a test asks how well posed a sequence's first read-outs are
+
+
 def mlstm(h, w, m, eps):
-    """Matrix memory with exponential gates kept in range by a running maximum (which starts at 0)."""
+    """Matrix memory with exponential gates kept in range by a running maximum (which starts at 0).  After one token
+    the memory holds one outer product, and what a head reads out, once scaled to unit size, is its value times the
+    SIGN of q . k: where that product is near zero, rounding decides.  `FIRST_ANGLES` collects |cos(q, k)| of the
+    first token, the smallest of the heads, for tests that choose a first token on which no rounding decides."""
     T = h.shape[0]
     H, dk, dv, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
     q = (h @ w["q"].T).view(T, H, dk) * dk ** -0.5
@@ -86,19 +112,9 @@ def mlstm(h, w, m, eps):
     v = (h @ w["v"].T).view(T, H, dv)
     li = capped(h @ w["i"].T + w["i.b"], cap)                       # [T, H] log input gate
     lf = logsigmoid(capped(h @ w["f"].T + w["f.b"], cap))           # [T, H] log forget gate
-    out = torch.zeros(T, H, dv, dtype=D)
-    for a in range(H):
-        S = torch.zeros(dk, dv, dtype=D)
-        n = torch.zeros(dk, dtype=D)
-        mx = torch.zeros((), dtype=D)
-        for t in range(T):
-            m_new = torch.maximum(lf[t, a] + mx, li[t, a])
-            keep, take = torch.exp(lf[t, a] + mx - m_new), torch.exp(li[t, a] - m_new)
-            S = keep * S + take * torch.outer(k[t, a], v[t, a])
-            n = keep * n + take * k[t, a]
-            mx = m_new
-            den = torch.maximum((n @ q[t, a]).abs(), torch.exp(-mx)) + 1e-6
-            out[t, a] = (S.T @ q[t, a]) / den
+    if FIRST_ANGLES is not None:
+        FIRST_ANGLES.append(((q[0] * k[0]).sum(-1).abs() / (q[0].norm(dim=-1) * k[0].norm(dim=-1)).clamp_min(1e-30)).min().item())
+    out = torch.stack([memory_walk(q[:, a], k[:, a], v[:, a], li[:, a], lf[:, a])[0] for a in range(H)], 1)
     y = unit(out, eps).reshape(T, H * dv) * w["norm"] * sigmoid(h @ w["g"].T)
     return y @ w["o"].T
 
