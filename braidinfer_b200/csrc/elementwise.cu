@@ -812,6 +812,7 @@ struct HeadPrepArgs {
     int page_size, table_cols, num_pages;
     float eps, temp_coef; int temp_every;
     int* error_flag;
+    int vec8;              // 16 bytes a lane (bfloat16, aligned heads of up to 256 numbers)
 };
 
 template <typename T>
@@ -840,6 +841,47 @@ head_prep_kv_kernel(HeadPrepArgs a) {
     const T* src = (const T*)a.src + (size_t)row * a.row_stride + col0;
     const int pos = a.positions[row];
     float f = 1.f;
+    if constexpr (sizeof(T) == 2) {
+        // 16 bytes a lane, the head read once and kept: heads of up to 256 numbers whose rows and sizes keep every
+        // head on a 16-byte boundary (the padded head then does too)
+        if (a.vec8) {
+            const int c = lane * 8;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (c < d) raw = *reinterpret_cast<const uint4*>(src + c);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 u = __bfloat1622float2(p2[j]); v[2 * j] = u.x; v[2 * j + 1] = u.y; }
+            if ((is_q || is_k) && a.unit) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+                ss = warp_sum(ss);
+                f = 1.f / sqrtf(ss / (float)d + a.eps);
+            }
+            if (is_q && a.temp_every > 0) f *= 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
+            T* dst8 = nullptr;
+            if (is_q) {
+                dst8 = (T*)a.q_out + ((size_t)row * a.nqh + head) * a.hd;
+            } else if (a.cache) {
+                const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+                const int block = pos / a.page_size, off = pos - block * a.page_size;
+                const int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+                if (page < 0 || page >= a.num_pages) {
+                    if (lane == 0) atomicExch(a.error_flag, 1);
+                    return;
+                }
+                dst8 = (T*)a.cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * a.nkh + kvh) * a.page_size + off) * a.hd;
+            }
+            if (!dst8 || c >= a.hd) return;
+            uint4 packed;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j] * f, v[2 * j + 1] * f);
+            *reinterpret_cast<uint4*>(dst8 + c) = packed;
+            return;
+        }
+    }
     if ((is_q || is_k) && a.unit) {
         float ss = 0.f;
         for (int c = lane; c < d; c += 32) { const float v = to_f32(src[c]); ss = fmaf(v, v, ss); }
@@ -872,8 +914,10 @@ extern "C" int braid_head_prep_kv(const void* src, long long row_stride, int dty
     if (nqh <= 0 || nkh <= 0 || dk <= 0 || dv <= 0 || hd < dk || hd < dv)
         BRAID_REFUSE("head_prep_kv: heads %d/%d of sizes %d and %d do not fit a padded head of %d", nqh, nkh, dk, dv, hd);
     if (cache && !page_table) BRAID_REFUSE("head_prep_kv: a cache write needs the step's page table");
+    const int vec8 = dtype == BRAID_BF16 && hd <= 256 && !(dk & 7) && !(dv & 7) && !(hd & 7) && !(row_stride & 7) &&
+                     !((uintptr_t)src & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)cache & 15);
     HeadPrepArgs a{src, row_stride, q_out, positions, token_seq, page_table, cache, rows, nqh, nkh, dk, dv, hd, unit,
-                   page_size, table_cols, num_pages, eps, temp_coef, temp_every, error_flag};
+                   page_size, table_cols, num_pages, eps, temp_coef, temp_every, error_flag, vec8};
     const long long blocks = ((long long)rows * (nqh + 2 * nkh) + 3) / 4;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("head_prep_kv: %d rows exceed one launch", rows);
     cudaStream_t s = (cudaStream_t)stream;

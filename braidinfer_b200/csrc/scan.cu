@@ -678,22 +678,44 @@ mlstm_gates_kernel(const float* __restrict__ z, long long z_stride, const T* __r
     float* mp = (float*)(state + (size_t)slot_ids[seq] * state_stride + state_offset) + h;
     float m = *mp;
     const float inv_cap = 1.f / cap;
+    // the next 32 tokens' logits are asked for before this group's chain is walked, so the chain hides their way
+    float zi_next = 0.f, zf_next = 0.f;
+    if (lane < n) {
+        const float* zr = z + (size_t)(r0 + lane) * z_stride;
+        zi_next = zr[h];
+        zf_next = zr[heads + h];
+    }
     for (int t0 = 0; t0 < n; t0 += 32) {
         const int t = t0 + lane;
+        const float zi = zi_next, zf = zf_next;
+        if (t + 32 < n) {
+            const float* zr = z + (size_t)(r0 + t + 32) * z_stride;
+            zi_next = zr[h];
+            zf_next = zr[heads + h];
+        }
         float li = 0.f, lf = 0.f;
         if (t < n) {
-            const float* zr = z + (size_t)(r0 + t) * z_stride;
-            li = cap * tanhf((zr[h] + b_i) * inv_cap);
-            const float x = cap * tanhf((zr[heads + h] + b_f) * inv_cap);
+            li = cap * tanhf((zi + b_i) * inv_cap);
+            const float x = cap * tanhf((zf + b_f) * inv_cap);
             lf = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
         }
         const int nt = min(32, n - t0);
         float m_prev = 0.f, m_mine = 0.f;
-        for (int l = 0; l < nt; ++l) {
-            const float f = __shfl_sync(0xffffffffu, lf, l), i = __shfl_sync(0xffffffffu, li, l);
-            const float mn = fmaxf(f + m, i);
-            if (l == lane) { m_prev = m; m_mine = mn; }
-            m = mn;
+        if (nt == 32) {                      // a full group: unrolled, so the broadcasts run ahead of the chain
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
+                const float f = __shfl_sync(0xffffffffu, lf, l), i = __shfl_sync(0xffffffffu, li, l);
+                const float mn = fmaxf(f + m, i);
+                if (l == lane) { m_prev = m; m_mine = mn; }
+                m = mn;
+            }
+        } else {
+            for (int l = 0; l < nt; ++l) {
+                const float f = __shfl_sync(0xffffffffu, lf, l), i = __shfl_sync(0xffffffffu, li, l);
+                const float mn = fmaxf(f + m, i);
+                if (l == lane) { m_prev = m; m_mine = mn; }
+                m = mn;
+            }
         }
         if (t < n) {
             float* o = out + (size_t)(r0 + t) * (3 * heads);
