@@ -252,6 +252,52 @@ def test_matrix_memory_whole_in_portions_and_token_by_token(K, dtype, heads, dk,
         assert (state[[0, 2]] == 255).all()                                   # the other slots were not touched
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_matrix_memory_of_a_long_prompt_keeps_a_token_from_its_start(K, dtype):
+    """300 tokens, walked whole (chunks side by side with a carry between them) and in portions that end on, just before
+    and just after the chunks' edges.  One token near the start has an open input gate and all others nearly closed
+    ones, with forget gates near one: every later read-out is that token's value, and a walk that lost it, or the
+    state at a chunk's or a portion's edge, returns something else."""
+    heads, dk, dv, cap, n, eps = 2, 32, 24, 10.0, 300, 1e-5
+    g = torch.Generator().manual_seed(11)
+    q, k = [dev(torch.randn(n, heads * dk, generator=g), dtype) for _ in range(2)]
+    v, gate = [dev(torch.randn(n, heads * dv, generator=g), dtype) for _ in range(2)]
+    k[2] = q[n - 1] = dev(torch.ones(heads * dk), dtype)
+    z = torch.cat([torch.full((n, heads), -6.0), torch.full((n, heads), 9.0)], 1)
+    z[2, :heads] = 8.0
+    z = z.cuda()
+    zero, w = dev(torch.zeros(heads), dtype), dev(1 + 0.3 * torch.randn(heads * dv, generator=g), dtype)
+    li, lf = P.capped(back(z)[:, :heads], cap), P.logsigmoid(P.capped(back(z)[:, heads:], cap))
+
+    def plain(vals):
+        o = [P.memory_walk(back(q)[:, a * dk:(a + 1) * dk] * dk ** -0.5, back(k)[:, a * dk:(a + 1) * dk],
+                           vals[:, a * dv:(a + 1) * dv], li[:, a], lf[:, a])[0] for a in range(heads)]
+        return P.unit(torch.stack(o, 1), eps).reshape(n, heads * dv) * back(w) * P.sigmoid(back(gate))
+
+    want = plain(back(v))
+    other = back(v).clone()
+    other[2] = -other[2]
+    assert rel(plain(other)[n - 1:], want[n - 1:]) > 0.5                       # the last read-out is token 2's value
+    m_off = heads * dk * (dv + 1) * 4
+    tol = 2e-5 if dtype == "float32" else 1.5e-2
+    for cuts in ([300], [128, 1, 63, 108], [127, 2, 171], [65, 63, 64, 108], [2, 298]):
+        state = torch.zeros(1, m_off + heads * 4, dtype=torch.uint8, device="cuda")
+        at = 0
+        for cut in cuts:
+            t = step_tables([cut], before=[at])
+            sl = slice(at, at + cut)
+            gates = torch.empty(t.rows, 3 * heads, dtype=torch.float32, device="cuda")
+            K.mlstm_gates(z[sl], zero, zero, gates, state, m_off, t, heads, cap)
+            o = torch.empty(t.rows, heads * (dv + 1), dtype=torch.float32, device="cuda")
+            K.linear_scan(q[sl], k[sl], v[sl], gates[:, :heads], zero, o, state, 0, t, heads, heads, dk, dv + 1, "given",
+                          q_scale=dk ** -0.5, kappa=gates[:, heads:2 * heads], v_cols=dv)
+            out = torch.zeros(t.rows, heads * dv, dtype=TORCH[dtype], device="cuda")
+            K.mlstm_out(o, gates[:, 2 * heads:], gate[sl], w, out, t.token_seq, heads, dv, eps)
+            assert rel(out[:cut], want[sl]) < tol, (cuts, cut)
+            at += cut
+    K.check_device_errors()
+
+
 def test_the_running_maximum_starts_at_zero_and_the_read_out_has_a_floor(K):
     """Input gates far below one at the first tokens: the maximum stays at 0 from its start (not at the first gate),
     and the read-out's denominator is its floor exp(-m); with a maximum that started at minus infinity the
