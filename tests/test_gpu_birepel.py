@@ -260,9 +260,10 @@ def test_matrix_memory_of_a_long_prompt_keeps_a_token_from_its_start(K, dtype):
     state at a chunk's or a portion's edge, returns something else."""
     heads, dk, dv, cap, n, eps = 2, 32, 24, 10.0, 300, 1e-5
     g = torch.Generator().manual_seed(11)
-    q, k = [dev(torch.randn(n, heads * dk, generator=g), dtype) for _ in range(2)]
+    # queries of one sign and that token's key all ones: no read-out is a sum that cancels, so rounding stays rounding
+    q, k = dev(torch.randn(n, heads * dk, generator=g).abs() + 0.1, dtype), dev(torch.randn(n, heads * dk, generator=g), dtype)
     v, gate = [dev(torch.randn(n, heads * dv, generator=g), dtype) for _ in range(2)]
-    k[2] = q[n - 1] = dev(torch.ones(heads * dk), dtype)
+    k[2] = dev(torch.ones(heads * dk), dtype)
     z = torch.cat([torch.full((n, heads), -6.0), torch.full((n, heads), 9.0)], 1)
     z[2, :heads] = 8.0
     z = z.cuda()
@@ -277,7 +278,7 @@ def test_matrix_memory_of_a_long_prompt_keeps_a_token_from_its_start(K, dtype):
     want = plain(back(v))
     other = back(v).clone()
     other[2] = -other[2]
-    assert rel(plain(other)[n - 1:], want[n - 1:]) > 0.5                       # the last read-out is token 2's value
+    assert rel(plain(other)[n - 1:], want[n - 1:]) > 0.5 and rel(plain(other)[150:151], want[150:151]) > 0.5     # token 2's value is read
     m_off = heads * dk * (dv + 1) * 4
     tol = 2e-5 if dtype == "float32" else 1.5e-2
     for cuts in ([300], [128, 1, 63, 108], [127, 2, 171], [65, 63, 64, 108], [2, 298]):
