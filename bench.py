@@ -417,7 +417,7 @@ def run_other_size(args):
 def run_sweep(args):
     """Decode at batch 1, 8, 64 over contexts of 512 to 32,768 tokens and prefill of 512 to 16,384
     tokens, on the default sizes: one JSON line with time, achieved bandwidth or FLOP rate, and the
-    fraction of the peak, for every point.  Not the contract's line."""
+    fraction of the peak, for every point.  Not the headline line."""
     import torch
     from braidinfer_b200.config import preset
     from braidinfer_b200.engine import Engine
@@ -471,7 +471,7 @@ def run_timeline(args):
     profiler (device activity only), printed as one JSON line: for the kernels of one layer in the
     middle of the step, the time from the end of the kernel before to the end of this one (kernels
     overlap their predecessors' tails through programmatic dependent launch, so durations would
-    count time twice).  Not the contract's line."""
+    count time twice).  Not the headline line."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     from braidinfer_b200.config import preset
@@ -522,7 +522,7 @@ def run_prompt_timeline(args):
     step of the default layer sizes (8 layers unless --layers says otherwise) under the torch profiler, and for the
     kernels of one layer in the middle the time from the end of the kernel before to the end of this one, as
     run_timeline does for a decode step.  Lengths up to 256 go through a CUDA graph from the third step on, as they
-    do in generation.  One JSON line a length.  Not the contract's line."""
+    do in generation.  One JSON line a length.  Not the headline line."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     from braidinfer_b200.config import preset
@@ -578,7 +578,7 @@ def run_chain(args):
     events (L2 flushed before each replay).  With BRAIDINFER_TRACE=1 in the environment the library is built with
     time stamps at the phase boundaries of the product and of the reduce + norm kernel (csrc/trace.cuh); the
     line then also carries, for the o product + reducer chain, the median over CTAs of every stamp, in
-    microseconds from the chain's first entry.  Not the contract's line."""
+    microseconds from the chain's first entry.  Not the headline line."""
     import ctypes
     import numpy as np
     import torch
@@ -1406,7 +1406,7 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch every step kernel by kernel")
     ap.add_argument("--preset", default="mistral_7b_v03",
                     choices=["mistral_7b_v03", "mistral_7b_v01", "mistral_nemo_12b"],
-                    help="the default is the contract's run; the other two print their own line (see run_other_size)")
+                    help="the default is the headline run; the other two print their own line (see run_other_size)")
     ap.add_argument("--sweep", action="store_true",
                     help="decode over batch and context, prefill over prompt length; prints its own line (see run_sweep)")
     ap.add_argument("--chain", action="store_true",
