@@ -38,7 +38,7 @@ class CacheGroup:
     def __init__(self, request: CacheRequest, entries: List[int], num_pages: int, dtype, device) -> None:
         self.request = request
         self.entries = entries                   # schedule entries that own a layer here
-        self.pages = GroupPages(num_pages, PAGE_SIZE, request.kind, request.window)
+        self.pages = GroupPages(num_pages, PAGE_SIZE, request.kind, request.window, request.keep_first)
         self.storage = torch.zeros((len(entries), num_pages, request.planes, request.num_kv_heads, PAGE_SIZE, request.head_dim),
                                    dtype=dtype, device=device)
 
@@ -108,7 +108,8 @@ class CacheManager:
                 f"{reader.num_kv_heads} kv heads of {reader.head_dim} and that cache holds "
                 f"{owner.num_kv_heads} of {owner.head_dim}")
         if owner.kind == "window":
-            if reader.kind != "window" or reader.window is None or reader.window > owner.window:
+            if (reader.kind != "window" or reader.window is None or reader.window > owner.window
+                    or reader.keep_first > owner.keep_first):
                 raise CacheError(
                     f"schedule entry {e} reads the cache of entry {owner_entry}, which keeps a window of "
                     f"{owner.window} positions only; the reader "

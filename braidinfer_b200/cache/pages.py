@@ -87,10 +87,12 @@ class GroupPages:
 
     kind "full" keeps every block; kind "window" gives back blocks that no later query
     can see: with window w, the next query (at position `length`) sees keys
-    j > length - w, so a block whose last position is <= length - w is dead.
+    j > length - w, so a block whose last position is <= length - w is dead.  With `keep_first` the blocks that
+    hold the sequence's first keep_first positions are never given back before the slot closes.
     """
 
-    def __init__(self, num_pages: int, page_size: int, kind: str = "full", window: Optional[int] = None) -> None:
+    def __init__(self, num_pages: int, page_size: int, kind: str = "full", window: Optional[int] = None,
+                 keep_first: int = 0) -> None:
         if kind not in ("full", "window"):
             raise CacheError(f"unknown cache kind {kind!r}")
         if kind == "window" and not window:
@@ -99,6 +101,7 @@ class GroupPages:
         self.page_size = page_size
         self.kind = kind
         self.window = window
+        self.keep_first = max(0, int(keep_first or 0))
         self.blocks: Dict[int, List[int]] = {}      # slot -> page per logical block (-1: released)
 
     def open(self, slot: int) -> None:
@@ -130,7 +133,8 @@ class GroupPages:
         b = self.blocks[slot]
         dead_upto = length - self.window            # positions <= this are never read again
         n_dead_blocks = max(0, (dead_upto + 1) // self.page_size)
-        for i in range(min(n_dead_blocks, len(b))):
+        kept_blocks = (self.keep_first + self.page_size - 1) // self.page_size
+        for i in range(kept_blocks, min(n_dead_blocks, len(b))):
             if b[i] >= 0:
                 self.pool.free(b[i])
                 b[i] = -1

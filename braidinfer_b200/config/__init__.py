@@ -4,6 +4,7 @@ from .mistral import MistralConfig
 from .bidinex import BidinexConfig
 from .loduzen import LoduzenConfig
 from .birepel import BirepelConfig
+from .ludazen import LudazenConfig
 from .presets import PRESETS, preset
 
 

@@ -162,7 +162,12 @@ class Kernels:
         L.braid_gather_i32.restype = c_int
         L.braid_attn_simple.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p]
+                                        c_float, c_int, c_float, c_float, c_void_p, c_void_p, c_longlong, c_int, c_void_p,
+                                        c_int, c_void_p, c_void_p]
+        L.braid_head_mix.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p] + \
+                                    [c_int] * 5 + [c_void_p]
+        L.braid_bias_xielu.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong] + [c_int] * 4 + \
+                                      [c_void_p]
         L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
         scale = [c_void_p, c_int, c_longlong, c_float, c_float]        # RowScale.args()
@@ -189,7 +194,7 @@ class Kernels:
                                 c_float, c_void_p]
         L.braid_softcap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         L.braid_concat2.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
-        for name in ("braid_dyt", "braid_softcap", "braid_concat2"):
+        for name in ("braid_dyt", "braid_softcap", "braid_concat2", "braid_head_mix", "braid_bias_xielu"):
             getattr(L, name).restype = c_int
         for name in ("braid_embed", "braid_embed_pos", "braid_head_prep_kv", "braid_head_gate", "braid_glu_clamp", "braid_rmsnorm", "braid_silu_mul", "braid_act_mul", "braid_head_norm_rope_kv",
                      "braid_act_mul_gather", "braid_rmsnorm_add", "braid_residual_add",
@@ -396,24 +401,58 @@ class Kernels:
                     positions: torch.Tensor, token_seq: torch.Tensor, nqh: int, nkh: int, hd: int,
                     page_size: int, window: Optional[int], scale: float, sink: Optional[float] = None,
                     out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
-                    head_gate: Optional[torch.Tensor] = None) -> None:
-        """q: [rows, >= nqh*hd] (a view of the qkv rows is fine), out: [rows, nqh*hd].  `sink`: the score of an
+                    head_gate: Optional[torch.Tensor] = None, keep_first: int = 0,
+                    head_scale: Optional[torch.Tensor] = None, value_heads: int = 1) -> None:
+        """q: [rows, >= nqh*hd] (a view of the qkv rows is fine), out: [rows, nqh*hd].  `keep_first`: with a window,
+        a sequence's first positions stay visible; `head_scale` (float32 [nqh]): a factor a head on the scores;
+        `value_heads` = nkh: every query head reads the values of every kv head, out is [rows, nqh*nkh*hd] with
+        the result of (head h, value head c) at virtual head h*nkh + c (see `head_mix`).  `sink`: the score of an
         attention sink, one more term of the softmax's denominator that has no value (None: no sink);
         `head_sinks` (float32 [nqh]): a sink score a head instead; `out_scale`: a constant factor on the result;
         `head_gate` ([rows, >= nqh] of the rows' type, a view is fine): head h's result times sigmoid(head_gate[row, h])."""
         rows = out.shape[0]
-        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype)
+        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype, head_scale)
+        if out.shape[1] < nqh * value_heads * hd:
+            raise KernelError("attn_simple: the result's rows do not hold the heads")
         self.launches += 1
         self._check(self.lib.braid_attn_simple(
             q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache.data_ptr(), page_table.data_ptr(),
             positions.data_ptr(), token_seq.data_ptr(), q.stride(0), out.stride(0), rows, nqh, nkh, hd,
             page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale),
             int(sink is not None), float(sink or 0.0), float(out_scale), _ptr(head_sinks), _ptr(head_gate),
-            head_gate.stride(0) if head_gate is not None else 0, self._error_flag.data_ptr() + 16, self._stream()),
+            head_gate.stride(0) if head_gate is not None else 0, int(keep_first or 0), _ptr(head_scale), int(value_heads),
+            self._error_flag.data_ptr() + 16, self._stream()),
             "attn_simple")
 
+    def head_mix(self, src: torch.Tensor, talk: torch.Tensor, out: torch.Tensor, token_seq: Optional[torch.Tensor],
+                 heads: int, kv_heads: int, hd: int, vd: int) -> None:
+        """out[row, h, :vd] = sum_g talk[h, g] * src[row, g * kv_heads + kv(h), :vd]: src [rows, heads * kv_heads * hd] is what
+        attention leaves when every head reads the values of every kv head, talk [heads, heads] mixes the heads'
+        probabilities after the softmax, out [rows, heads * vd].  float32 sums; rows of padding come out zero."""
+        rows = src.shape[0]
+        if src.stride(1) != 1 or out.stride(1) != 1 or src.shape[1] < heads * kv_heads * hd or out.shape[1] < heads * vd \
+                or src.dtype != out.dtype or tuple(talk.shape) != (heads, heads) or not talk.is_contiguous():
+            raise KernelError("head_mix: src [rows, heads * kv_heads * hd], talk contiguous [heads, heads], out [rows, heads * vd]")
+        self.launches += 1
+        self._check(self.lib.braid_head_mix(src.data_ptr(), src.stride(0), talk.data_ptr(), dtype_code(talk.dtype),
+                                            out.data_ptr(), out.stride(0), dtype_code(out.dtype), _ptr(token_seq), rows, heads,
+                                            kv_heads, hd, vd, self._stream()), "head_mix")
+
+    def bias_xielu(self, z: torch.Tensor, bias: torch.Tensor, pq: torch.Tensor, out: torch.Tensor, n: int) -> None:
+        """out[:, :n] = f(z[:, :n] + bias) with the two-piece activation f of pointwise.cu, whose numbers (p, q) are the
+        stored tensor `pq`; the further columns of out become 1, 0, 0, ... (a bias column for the product that reads it)."""
+        if z.stride(1) != 1 or out.stride(1) != 1 or z.shape[1] < n or out.shape[1] < n or z.dtype != out.dtype \
+                or bias.numel() != n or pq.numel() != 2 or bias.dtype != pq.dtype or z.shape[0] != out.shape[0]:
+            raise KernelError("bias_xielu: z [rows, >= n], bias [n], pq [2] of one type, out [rows, >= n] of z's type")
+        self.launches += 1
+        self._check(self.lib.braid_bias_xielu(z.data_ptr(), z.stride(0), bias.data_ptr(), pq.data_ptr(), dtype_code(bias.dtype),
+                                              out.data_ptr(), out.stride(0), dtype_code(out.dtype), z.shape[0], n, out.shape[1],
+                                              self._stream()), "bias_xielu")
+
     @staticmethod
-    def _check_head_extras(head_sinks, head_gate, nqh: int, dtype) -> None:
+    def _check_head_extras(head_sinks, head_gate, nqh: int, dtype, head_scale=None) -> None:
+        if head_scale is not None and (head_scale.dtype != torch.float32 or head_scale.numel() != nqh or not head_scale.is_contiguous()):
+            raise KernelError(f"attention: a factor a head is a contiguous float32 tensor of {nqh} numbers")
         if head_sinks is not None and (head_sinks.dtype != torch.float32 or head_sinks.numel() != nqh or not head_sinks.is_contiguous()):
             raise KernelError(f"attention: a sink a head is a contiguous float32 tensor of {nqh} scores")
         if head_gate is not None and (head_gate.dtype != dtype or head_gate.stride(1) != 1 or head_gate.shape[1] < nqh):
@@ -557,7 +596,7 @@ class Kernels:
             lib.braid_last_error.restype = c_char_p
             if name == "latent":
                 lib.braid_latent_prep.argtypes = [c_void_p, c_longlong, c_int] + [c_void_p] * 7 + [c_int] * 10 + \
-                                                 [c_float, c_void_p, c_void_p]
+                                                 [c_float, c_int, c_void_p, c_void_p]
                 lib.braid_gemm_heads.argtypes = [c_void_p] * 4 + [c_int] * 5 + [c_longlong] * 5 + [c_float, c_void_p]
                 lib.braid_gemm_heads_mma.argtypes = [c_void_p] * 4 + [c_int] * 4 + [c_longlong] * 5 + [c_float, c_void_p]
                 lib.braid_gemm_heads_mma.restype = c_int
@@ -583,13 +622,14 @@ class Kernels:
                 names = ("braid_causal_conv", "braid_linear_scan", "braid_gated_norm", "braid_scan_decay", "braid_mlstm_gates",
                          "braid_mlstm_out")
             elif name == "moe":
-                lib.braid_moe_route.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_float, c_void_p]
+                lib.braid_moe_route.argtypes = [c_void_p] * 3 + [c_int] * 5 + [c_float, c_int, c_void_p]
                 lib.braid_moe_plan.argtypes = [c_void_p] * 6 + [c_int] * 5 + [c_void_p]
                 lib.braid_moe_gemm_simt.argtypes = [c_void_p] * 7 + [c_int, c_int, c_longlong, c_longlong] + [c_int] * 5 + \
-                                                   [c_void_p]
+                                                   [c_void_p, c_void_p]
                 lib.braid_moe_combine.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                   c_longlong, c_void_p]
-                lib.braid_moe_gemm_mma.argtypes = [c_void_p] * 7 + [c_int, c_longlong, c_longlong] + [c_int] * 5 + [c_void_p]
+                lib.braid_moe_gemm_mma.argtypes = [c_void_p] * 7 + [c_int, c_longlong, c_longlong] + [c_int] * 5 + \
+                                                  [c_void_p, c_void_p]
                 lib.braid_moe_gemm_mma.restype = c_int
                 names = ("braid_moe_route", "braid_moe_plan", "braid_moe_gemm_simt", "braid_moe_combine")
             else:
@@ -608,12 +648,16 @@ class Kernels:
     def latent_prep(self, proj: torch.Tensor, q_cols: int, norm_w: torch.Tensor, inv_freq: torch.Tensor,
                     positions: torch.Tensor, token_seq: torch.Tensor, page_table: Optional[torch.Tensor],
                     cache: Optional[torch.Tensor], q_lat: torch.Tensor, heads: int, dim: int, rot: int, rank: int,
-                    rot_dims: int, page_size: int, eps: float) -> None:
+                    rot_dims: int, page_size: int, eps: float, adjacent: bool = False) -> None:
         """A step's projected rows [rows, heads*(dim+rot) + rank + rot (+ more)]: the latent part is RMS-normed and,
         with the rotated shared key part, written into `cache` ([pages, 1, 1, page_size, rank + rot]); the rotated
         parts of the queries are written into q_lat[:, :, rank:] ([rows, heads, rank + rot])."""
         lib = self.part_library("latent")
-        if norm_w.dtype != proj.dtype or q_lat.dtype != proj.dtype or (cache is not None and cache.dtype != proj.dtype):
+        if cache is None:
+            norm_w = None                       # no latent is made: the rows need not hold one
+        elif norm_w is None:
+            raise KernelError("latent_prep: the latent's norm weight is missing")
+        if (norm_w is not None and norm_w.dtype != proj.dtype) or q_lat.dtype != proj.dtype or (cache is not None and cache.dtype != proj.dtype):
             raise KernelError("latent_prep: rows, norm weight, queries and cache must have one element type")
         if not q_lat.is_contiguous() or tuple(q_lat.shape) != (proj.shape[0], heads, rank + rot):
             raise KernelError(f"latent_prep: q_lat must be contiguous [{proj.shape[0]}, {heads}, {rank + rot}]")
@@ -623,10 +667,10 @@ class Kernels:
         cols = page_table.shape[1] if page_table is not None else 0
         self.launches += 1
         self._check_lib(lib, lib.braid_latent_prep(
-            proj.data_ptr(), proj.stride(0), q_cols, norm_w.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(),
+            proj.data_ptr(), proj.stride(0), q_cols, _ptr(norm_w), inv_freq.data_ptr(), positions.data_ptr(),
             token_seq.data_ptr(), _ptr(page_table), _ptr(cache), q_lat.data_ptr(), dtype_code(proj.dtype),
             proj.shape[0], heads, dim, rot, rank, rot_dims, page_size, cols, cache.shape[0] if cache is not None else 0,
-            float(eps), self._error_flag.data_ptr(), self._stream()), "latent_prep")
+            float(eps), int(adjacent), self._error_flag.data_ptr(), self._stream()), "latent_prep")
 
     def gemm_heads(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
                    mult: float = 1.0, tensor_cores: bool = True) -> None:
@@ -679,9 +723,10 @@ class Kernels:
 
     # ------------------------------------------------------------------ mixture of experts
     def moe_route(self, logits: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor, groups: int, keep: int,
-                  mult: float = 1.0) -> None:
+                  mult: float = 1.0, sigmoid: bool = False) -> None:
         """Router logits [rows, experts] (float32) -> for each row its `top` experts idx [rows, top] (int32, by falling
-        score) and their weights wgt [rows, top] (float32): softmax scores of the chosen, over their sum, times mult."""
+        score) and their weights wgt [rows, top] (float32): softmax scores of the chosen, over their sum, times mult;
+        with `sigmoid` the scores are sigmoids of the logits and the weights the chosen scores as they are, times mult."""
         lib = self.part_library("moe")
         rows, experts = logits.shape
         top = idx.shape[1]
@@ -690,7 +735,7 @@ class Kernels:
             raise KernelError("moe_route: logits float32 [rows, experts], idx int32 and wgt float32 [rows, top], contiguous")
         self.launches += 1
         self._check_lib(lib, lib.braid_moe_route(logits.data_ptr(), idx.data_ptr(), wgt.data_ptr(), rows, experts, top,
-                                                 groups, keep, float(mult), self._stream()), "moe_route")
+                                                 groups, keep, float(mult), int(sigmoid), self._stream()), "moe_route")
 
     @staticmethod
     def moe_max_tiles(rows: int, top: int, experts: int, tile: int) -> int:
@@ -717,8 +762,9 @@ class Kernels:
         return slot_pair, pair_slot, tile_expert, meta, max_tiles
 
     def moe_gemm_simt(self, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], out: torch.Tensor, plan,
-                      top: int, tile: int, relu2: bool = False) -> None:
-        """The experts' products over a plan's slots, plain.  With w1: out[slot] = silu(w0[e] x[row]) * (w1[e] x[row]),
+                      top: int, tile: int, relu2: bool = False, in_wgt: Optional[torch.Tensor] = None) -> None:
+        """`in_wgt` (float32 [rows, top], with w1): a pair's weight multiplies the expert's input, that is gate and up
+        before the activation.  The experts' products over a plan's slots, plain.  With w1: out[slot] = silu(w0[e] x[row]) * (w1[e] x[row]),
         x the step's rows; without: out[slot] = w0[e] x[slot], x a tensor of slots; with `relu2` (and no w1):
         out[slot] = relu(w0[e] x[row])^2, x the step's rows (experts without a gate).  w0, w1 [experts, J, K]."""
         lib = self.part_library("moe")
@@ -734,7 +780,15 @@ class Kernels:
         self._check_lib(lib, lib.braid_moe_gemm_simt(
             x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
             meta.data_ptr(), dtype_code(x.dtype), self._moe_mode(w1, relu2), x.stride(0), out.stride(0), j, k, top, tile,
-            max_tiles, self._stream()), "moe_gemm_simt")
+            max_tiles, self._in_wgt(in_wgt, x, top, w1), self._stream()), "moe_gemm_simt")
+
+    @staticmethod
+    def _in_wgt(in_wgt, x, top: int, w1):
+        if in_wgt is None:
+            return None
+        if w1 is None or in_wgt.dtype != torch.float32 or not in_wgt.is_contiguous() or tuple(in_wgt.shape) != (x.shape[0], top):
+            raise KernelError("moe_gemm: the weights on the experts' input are float32 [rows, top] and go with the gated product")
+        return in_wgt.data_ptr()
 
     @staticmethod
     def _moe_mode(w1, relu2: bool) -> int:
@@ -748,7 +802,7 @@ class Kernels:
                 and x.data_ptr() % 16 == 0 and w0.data_ptr() % 16 == 0 and tile in (16, 64))
 
     def moe_gemm_mma(self, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], out: torch.Tensor, plan,
-                     top: int, tile: int, relu2: bool = False) -> None:
+                     top: int, tile: int, relu2: bool = False, in_wgt: Optional[torch.Tensor] = None) -> None:
         """`moe_gemm_simt` in bfloat16 on the tensor cores; the plan's tile (16 or 64 slots) is the CTA's."""
         lib = self.part_library("moe")
         slot_pair, _pair_slot, tile_expert, meta, max_tiles = plan
@@ -763,7 +817,7 @@ class Kernels:
         self._check_lib(lib, lib.braid_moe_gemm_mma(
             x.data_ptr(), w0.data_ptr(), _ptr(w1), out.data_ptr(), slot_pair.data_ptr(), tile_expert.data_ptr(),
             meta.data_ptr(), self._moe_mode(w1, relu2), x.stride(0), out.stride(0), j, k, top, tile, max_tiles,
-            self._stream()), "moe_gemm_mma")
+            self._in_wgt(in_wgt, x, top, w1), self._stream()), "moe_gemm_mma")
 
     @staticmethod
     def attn_latent_mma_supports(rank: int, rot: int) -> bool:
@@ -829,15 +883,17 @@ class Kernels:
             page_table.shape[1], cache.shape[0], int(window or 0), n_splits, float(scale),
             self._error_flag.data_ptr() + 16, self._stream()), "attn_latent_mma")
 
-    def moe_combine(self, h: torch.Tensor, y: torch.Tensor, plan, wgt: torch.Tensor) -> None:
-        """h[row] += sum_k wgt[row, k] * y[slot of (row, k)], float32, choices added in their order."""
+    def moe_combine(self, h: torch.Tensor, y: torch.Tensor, plan, wgt: Optional[torch.Tensor], top: Optional[int] = None) -> None:
+        """h[row] += sum_k wgt[row, k] * y[slot of (row, k)], float32, choices added in their order (wgt None: every
+        weight is 1, and `top` says how many choices a row has)."""
         lib = self.part_library("moe")
         rows, width = h.shape
         if h.dtype != torch.float32 or not h.is_contiguous() or y.shape[1] != width or y.stride(1) != 1:
             raise KernelError("moe_combine: h is the contiguous float32 residual stream, y [slots, width]")
         self.launches += 1
         self._check_lib(lib, lib.braid_moe_combine(h.data_ptr(), y.data_ptr(), dtype_code(y.dtype), plan[1].data_ptr(),
-                                                   wgt.data_ptr(), rows, width, wgt.shape[1], y.stride(0), self._stream()),
+                                                   _ptr(wgt), rows, width, wgt.shape[1] if wgt is not None else int(top),
+                                                   y.stride(0), self._stream()),
                         "moe_combine")
 
     # ------------------------------------------------------------------ mixers with a recurrent state

@@ -31,6 +31,7 @@ struct LatentPrepArgs {
     int page_size, table_cols, num_pages;
     float eps;
     int* error_flag;
+    int adjacent;             // pairs are (2p, 2p + 1) instead of (p, p + rot_dims/2)
 };
 
 template <typename T>
@@ -56,19 +57,23 @@ latent_prep_kernel(LatentPrepArgs a) {
             dst = (T*)a.cache + ((size_t)page * a.page_size + off) * D;
         }
     }
-    // c = x / sqrt(mean(x^2) + eps) * w
+    // c = x / sqrt(mean(x^2) + eps) * w  (only where there is a cache to write: a layer that reads another layer's
+    // latent has no c and no kr in its rows)
     float ss = 0.f;
-    for (int i = threadIdx.x; i < a.rank; i += blockDim.x) {
-        const float v = to_f32(cin[i]);
-        ss = fmaf(v, v, ss);
+    if (a.cache) {
+        for (int i = threadIdx.x; i < a.rank; i += blockDim.x) {
+            const float v = to_f32(cin[i]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, red);
     }
-    ss = block_sum(ss, red);
     const float scale = 1.f / sqrtf(ss / (float)a.rank + a.eps);
     if (dst) {
         const T* w = (const T*)a.norm_w;
         for (int i = threadIdx.x; i < a.rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(cin[i]) * scale * to_f32(w[i]));
     }
-    // rotation: element i pairs with i + rot_dims/2; vector 0 is the shared key part, 1.. are the heads' queries
+    // rotation: element i pairs with i + rot_dims/2 (or, `adjacent`, 2i with 2i + 1); vector 0 is the shared key
+    // part, 1.. are the heads' queries
     const int half = a.rot_dims / 2;
     const int per = half + (a.rot - a.rot_dims);           // work items a vector: pairs, then untouched elements
     for (int e = threadIdx.x; e < (a.heads + 1) * per; e += blockDim.x) {
@@ -79,9 +84,10 @@ latent_prep_kernel(LatentPrepArgs a) {
         if (p < half) {
             float sn, cs;
             sincosf((float)pos * a.inv_freq[p], &sn, &cs);
-            const float x0 = to_f32(in[p]), x1 = to_f32(in[p + half]);
-            out[p] = from_f32<T>(x0 * cs - x1 * sn);
-            out[p + half] = from_f32<T>(x1 * cs + x0 * sn);
+            const int i0 = a.adjacent ? 2 * p : p, i1 = a.adjacent ? 2 * p + 1 : p + half;
+            const float x0 = to_f32(in[i0]), x1 = to_f32(in[i1]);
+            out[i0] = from_f32<T>(x0 * cs - x1 * sn);
+            out[i1] = from_f32<T>(x1 * cs + x0 * sn);
         } else {
             const int i = a.rot_dims + (p - half);
             out[i] = in[i];
@@ -92,14 +98,14 @@ latent_prep_kernel(LatentPrepArgs a) {
 extern "C" int braid_latent_prep(const void* proj, long long ld, int q_cols, const void* norm_w, const float* inv_freq,
                                  const int* positions, const int* token_seq, const int* page_table, void* cache,
                                  void* q_lat, int dtype, int rows, int heads, int dim, int rot, int rank, int rot_dims,
-                                 int page_size, int table_cols, int num_pages, float eps, int* error_flag, void* stream) {
+                                 int page_size, int table_cols, int num_pages, float eps, int adjacent, int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (heads <= 0 || dim < 0 || rot < 0 || rank <= 0) BRAID_REFUSE("latent_prep: heads=%d dim=%d rot=%d rank=%d", heads, dim, rot, rank);
     if (rot_dims < 0 || rot_dims > rot || rot_dims % 2) BRAID_REFUSE("latent_prep: %d rotated dimensions must be even and within %d", rot_dims, rot);
     if (!error_flag) BRAID_REFUSE("latent_prep: error_flag is required");
     if (cache && (!page_table || table_cols <= 0 || num_pages <= 0 || page_size <= 0)) BRAID_REFUSE("latent_prep: the cache has no pages");
     LatentPrepArgs a{proj, ld, q_cols, norm_w, inv_freq, positions, token_seq, page_table, cache, q_lat,
-                     rows, heads, dim, rot, rank, rot_dims, page_size, table_cols, num_pages, eps, error_flag};
+                     rows, heads, dim, rot, rank, rot_dims, page_size, table_cols, num_pages, eps, error_flag, adjacent};
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == BRAID_F32) braid_launch(latent_prep_kernel<float>, dim3(rows), dim3(128), 0, s, a);
     else if (dtype == BRAID_BF16) braid_launch(latent_prep_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, a);

@@ -5,7 +5,9 @@
 // neighbours, a group's score is its largest s, and only experts of the `keep` best groups can be chosen;
 // the `top` allowed experts with the largest s are chosen (ties: the lower index); their weights are
 // their s divided by the sum of the chosen s (+ 1e-20), times `mult` (a constant factor the caller wants
-// on the layer's output).  Everything float32.
+// on the layer's output).  Everything float32.  `sigmoid` routing instead scores every expert by itself,
+// s = 1 / (1 + exp(-z)), chooses the same way, and leaves the chosen scores as the weights (times `mult`), not
+// renormalised.
 //
 // The plan: every chosen (token, choice) pair gets a slot in an array ordered by expert, each expert's run
 // padded to a multiple of `tile` slots, so that a tile of slots belongs to one expert and the products can
@@ -22,6 +24,7 @@ struct MoeRouteArgs {
     float* wgt;               // [rows, top]
     int rows, experts, top, groups, keep;
     float mult;
+    int sigmoid;              // scores are sigmoids of the logits and the weights are the chosen scores as they are
 };
 
 #define MOE_ROUTE_WARPS 4
@@ -37,18 +40,22 @@ moe_route_kernel(MoeRouteArgs a) {
     float* s = smem + (size_t)warp * (a.experts + a.groups);
     float* gs = s + a.experts;
     const float* z = a.logits + (size_t)row * a.experts;
-    float mx = -INFINITY;
-    for (int e = lane; e < a.experts; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < a.experts; e += 32) {
-        const float p = expf(z[e] - mx);
-        s[e] = p;
-        sum += p;
+    if (a.sigmoid) {
+        for (int e = lane; e < a.experts; e += 32) s[e] = 1.f / (1.f + expf(-z[e]));
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < a.experts; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < a.experts; e += 32) {
+            const float p = expf(z[e] - mx);
+            s[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.f / sum;
+        for (int e = lane; e < a.experts; e += 32) s[e] *= inv;
     }
-    sum = warp_sum(sum);
-    const float inv = 1.f / sum;
-    for (int e = lane; e < a.experts; e += 32) s[e] *= inv;
     __syncwarp();
     const int per = a.experts / a.groups;
     for (int g = lane; g < a.groups; g += 32) {
@@ -99,19 +106,19 @@ moe_route_kernel(MoeRouteArgs a) {
         chosen_sum += best;
         __syncwarp();
     }
-    const float norm = a.mult / (chosen_sum + 1e-20f);
+    const float norm = a.sigmoid ? a.mult : a.mult / (chosen_sum + 1e-20f);
     __syncwarp();
     for (int k = lane; k < a.top; k += 32) a.wgt[(size_t)row * a.top + k] *= norm;
 }
 
 extern "C" int braid_moe_route(const float* logits, int* idx, float* wgt, int rows, int experts, int top,
-                               int groups, int keep, float mult, void* stream) {
+                               int groups, int keep, float mult, int sigmoid, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (experts <= 0 || top <= 0 || top > experts) BRAID_REFUSE("moe_route: top=%d of %d experts", top, experts);
     if (groups <= 0 || experts % groups || keep <= 0 || keep > groups) BRAID_REFUSE("moe_route: %d experts in %d groups, %d kept", experts, groups, keep);
     const size_t smem = (size_t)MOE_ROUTE_WARPS * (experts + groups) * sizeof(float);
     if (smem > 48 * 1024) BRAID_REFUSE("moe_route: %d experts are more than one block's shared memory holds", experts);
-    MoeRouteArgs a{logits, idx, wgt, rows, experts, top, groups, keep, mult};
+    MoeRouteArgs a{logits, idx, wgt, rows, experts, top, groups, keep, mult, sigmoid};
     braid_launch(moe_route_kernel, dim3((rows + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS), dim3(MOE_ROUTE_WARPS * 32), smem,
                  (cudaStream_t)stream, a);
     BRAID_LAUNCH_CHECK();
@@ -182,6 +189,9 @@ extern "C" int braid_moe_plan(const int* idx, const int* token_seq, int* slot_pa
 // order along k.  MODE 0: act[slot, j] = silu(x[token] . gate_e[j]) * (x[token] . up_e[j]), the input rows
 // gathered through slot_pair.  MODE 1: y[slot, j] = act[slot] . down_e[j].  MODE 2 (experts without a gate):
 // act[slot, j] = relu(x[token] . up_e[j])^2, the input rows gathered like MODE 0's, w0 the up matrices.
+// With `in_wgt` (MODE 0) a pair's weight multiplies the expert's input instead of its output: the expert sees w x, and
+// since its first products are linear, gate and up are multiplied by w in float32 before the activation,
+// act = silu(w (x . gate)) * (w (x . up)); the weighted sum then adds the pairs with weight 1.
 struct MoeGemmArgs {
     const void* x;            // MODE 0: [rows, ldx] the layer's normed input; MODE 1: act [slots, ldx]
     const void* w0;           // MODE 0: gate [experts, J, K]; MODE 1: down [experts, J, K]
@@ -192,6 +202,7 @@ struct MoeGemmArgs {
     const int* meta;
     long long ldx, ldo;
     int J, K, top, tile;
+    const float* in_wgt;      // MODE 0: [rows * top] a weight a pair on the expert's input; or null
 };
 
 template <typename T, int MODE>
@@ -247,8 +258,9 @@ moe_gemm_simt_kernel(MoeGemmArgs a) {
         const int m = m0 + tj * 4 + j;
         if (m >= a.J) continue;
         if (MODE == 0) {
-            const float g = acc0[j];
-            o[m] = from_f32<T>(my_pair >= 0 ? g / (1.f + expf(-g)) * acc1[j] : 0.f);
+            const float wi = (a.in_wgt && my_pair >= 0) ? a.in_wgt[my_pair] : 1.f;
+            const float g = acc0[j] * wi;
+            o[m] = from_f32<T>(my_pair >= 0 ? g / (1.f + expf(-g)) * (acc1[j] * wi) : 0.f);
         } else if (MODE == 2) {
             const float r = fmaxf(acc0[j], 0.f);
             o[m] = from_f32<T>(my_pair >= 0 ? r * r : 0.f);
@@ -260,11 +272,13 @@ moe_gemm_simt_kernel(MoeGemmArgs a) {
 
 extern "C" int braid_moe_gemm_simt(const void* x, const void* w0, const void* w1, void* out, const int* slot_pair,
                                    const int* tile_expert, const int* meta, int dtype, int mode, long long ldx,
-                                   long long ldo, int J, int K, int top, int tile, int max_tiles, void* stream) {
+                                   long long ldo, int J, int K, int top, int tile, int max_tiles, const float* in_wgt,
+                                   void* stream) {
     if (max_tiles <= 0 || J <= 0) return BRAID_OK;
     if (K <= 0) BRAID_REFUSE("moe_gemm: k=%d must be positive", K);
     if (tile <= 0 || tile % 16) BRAID_REFUSE("moe_gemm: the tile of %d slots must be a multiple of 16", tile);
-    MoeGemmArgs a{x, w0, w1, out, slot_pair, tile_expert, meta, ldx, ldo, J, K, top, tile};
+    if (in_wgt && mode != 0) BRAID_REFUSE("moe_gemm: a weight on the expert's input goes with the gated first product (mode 0)");
+    MoeGemmArgs a{x, w0, w1, out, slot_pair, tile_expert, meta, ldx, ldo, J, K, top, tile, in_wgt};
     const long long units = (long long)max_tiles * (tile / 16);
     if (units > 65535) BRAID_REFUSE("moe_gemm: %lld units of 16 slots exceed the grid limit", units);
     dim3 grid((J + 63) / 64, (unsigned)units);
@@ -331,15 +345,17 @@ moe_gemm_mma_kernel(MoeGemmArgs a) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int slot = slot0 + wm0 + mi * 16 + (lane >> 2) + half * 8;
-            const bool live = MODE == 1 || a.slot_pair[slot] >= 0;
+            const int pair_here = MODE == 1 ? 0 : a.slot_pair[slot];
+            const bool live = pair_here >= 0;
+            const float wi = (MODE == 0 && a.in_wgt && live) ? a.in_wgt[pair_here] : 1.f;
 #pragma unroll
             for (int ni = 0; ni < Tile::NI; ++ni) {
                 const int col = m0 + wn0 + ni * 8 + 2 * (lane & 3);
                 float v0, v1;
                 if (MODE == 0) {
-                    const float g0 = acc[0][mi][ni][half * 2], g1 = acc[0][mi][ni][half * 2 + 1];
-                    v0 = live ? g0 / (1.f + expf(-g0)) * acc[NB - 1][mi][ni][half * 2] : 0.f;
-                    v1 = live ? g1 / (1.f + expf(-g1)) * acc[NB - 1][mi][ni][half * 2 + 1] : 0.f;
+                    const float g0 = acc[0][mi][ni][half * 2] * wi, g1 = acc[0][mi][ni][half * 2 + 1] * wi;
+                    v0 = live ? g0 / (1.f + expf(-g0)) * (acc[NB - 1][mi][ni][half * 2] * wi) : 0.f;
+                    v1 = live ? g1 / (1.f + expf(-g1)) * (acc[NB - 1][mi][ni][half * 2 + 1] * wi) : 0.f;
                 } else if (MODE == 2) {
                     const float r0 = fmaxf(acc[0][mi][ni][half * 2], 0.f), r1 = fmaxf(acc[0][mi][ni][half * 2 + 1], 0.f);
                     v0 = live ? r0 * r0 : 0.f;
@@ -360,13 +376,14 @@ moe_gemm_mma_kernel(MoeGemmArgs a) {
 
 extern "C" int braid_moe_gemm_mma(const void* x, const void* w0, const void* w1, void* out, const int* slot_pair,
                                   const int* tile_expert, const int* meta, int mode, long long ldx, long long ldo,
-                                  int J, int K, int top, int tile, int max_tiles, void* stream) {
+                                  int J, int K, int top, int tile, int max_tiles, const float* in_wgt, void* stream) {
     if (max_tiles <= 0 || J <= 0) return BRAID_OK;
     if (K <= 0 || K % 8 || ldx % 8) BRAID_REFUSE("moe_gemm_mma: k=%d and the row stride %lld must be multiples of 8", K, ldx);
     if (((uintptr_t)x | (uintptr_t)w0 | (uintptr_t)w1) & 15) BRAID_REFUSE("moe_gemm_mma: operands must start on 16 bytes");
     if (tile != 16 && tile != 64) BRAID_REFUSE("moe_gemm_mma: the plan's tile must be 16 or 64 slots, not %d", tile);
     if (max_tiles > 65535) BRAID_REFUSE("moe_gemm_mma: %d tiles exceed the grid limit", max_tiles);
-    MoeGemmArgs a{x, w0, w1, out, slot_pair, tile_expert, meta, ldx, ldo, J, K, top, tile};
+    if (in_wgt && mode != 0) BRAID_REFUSE("moe_gemm: a weight on the expert's input goes with the gated first product (mode 0)");
+    MoeGemmArgs a{x, w0, w1, out, slot_pair, tile_expert, meta, ldx, ldo, J, K, top, tile, in_wgt};
     cudaStream_t s = (cudaStream_t)stream;
     // the down product over tiles of 64 slots takes 128 outputs a CTA (its rows are fetched half as often: 0.36 -> 0.29 ms
     // at 2,048 tokens of width 2048); gate+up with its two accumulators stays at 64 (at 128 it needs 237 registers and
@@ -396,7 +413,8 @@ extern "C" int braid_moe_gemm_mma(const void* x, const void* w0, const void* w1,
 }
 
 // ------------------------------------------------------------------ the weighted sum
-// h[row, :] += sum over the row's choices k, in the order of k, of wgt[row, k] * y[pair_slot[row, k], :].
+// h[row, :] += sum over the row's choices k, in the order of k, of wgt[row, k] * y[pair_slot[row, k], :]
+// (wgt null: every weight is 1, for experts whose weight went into their input).
 template <typename T>
 __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ y, const int* __restrict__ pair_slot,
                                    const float* __restrict__ wgt, int rows, int width, int top, long long ldy) {
@@ -407,7 +425,7 @@ __global__ void moe_combine_kernel(float* __restrict__ h, const T* __restrict__ 
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
             const int slot = pair_slot[(size_t)row * top + k];
-            if (slot >= 0) acc = fmaf(wgt[(size_t)row * top + k], to_f32(y[(size_t)slot * ldy + c]), acc);
+            if (slot >= 0) acc = fmaf(wgt ? wgt[(size_t)row * top + k] : 1.f, to_f32(y[(size_t)slot * ldy + c]), acc);
         }
         h[(size_t)row * width + c] += acc;
     }

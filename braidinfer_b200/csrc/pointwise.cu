@@ -158,3 +158,91 @@ extern "C" int braid_rmsnorm_add(float* h, const float* y, const void* w, int w_
     else BRAID_REFUSE("rmsnorm_add: unknown dtype code %d", w_dtype);
     BRAID_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ a mix of the heads after the softmax
+// Attention whose probabilities are mixed across the heads before they meet the values,
+//     p'_h(i, j) = sum_g talk[h, g] p_g(i, j),      out_h(i) = sum_j p'_h(i, j) v_kv(h)(j),
+// is linear in the probabilities, so out_h = sum_g talk[h, g] O[g, kv(h)] with O[g, c] = sum_j p_g(i, j) v_c(j): what the
+// attention kernels leave at virtual head g * kv_heads + c when every query head reads the values of every kv head.
+// src [rows, heads * kv_heads, hd] -> out [rows, heads, vd] (the first vd numbers of a head: heads may be padded).
+// The sum over g is float32, in the order of g.
+template <typename T, typename TW>
+__global__ void head_mix_kernel(const T* __restrict__ src, long long lds, const TW* __restrict__ talk, T* __restrict__ out,
+                                long long ldo, const int* __restrict__ token_seq, int heads, int kvh, int hd, int vd) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const bool padding = token_seq && token_seq[row] < 0;
+    const int group = heads / kvh;
+    const T* s = src + (size_t)row * lds;
+    T* o = out + (size_t)row * ldo;
+    for (int i = threadIdx.x; i < heads * vd; i += blockDim.x) {
+        const int h = i / vd, d = i - h * vd;
+        float acc = 0.f;
+        if (!padding) {
+            const int c = h / group;
+            for (int g = 0; g < heads; ++g)
+                acc = fmaf(to_f32(talk[h * heads + g]), to_f32(s[((size_t)g * kvh + c) * hd + d]), acc);
+        }
+        o[i] = from_f32<T>(acc);
+    }
+}
+
+extern "C" int braid_head_mix(const void* src, long long lds, const void* talk, int talk_dtype, void* out, long long ldo,
+                              int dtype, const int* token_seq, int rows, int heads, int kvh, int hd, int vd, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (heads <= 0 || kvh <= 0 || heads % kvh || vd <= 0 || vd > hd) BRAID_REFUSE("head_mix: heads=%d kv heads=%d head size=%d value size=%d", heads, kvh, hd, vd);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = heads * vd >= 1024 ? 256 : 128;
+#define BRAID_MIX(T, TW) braid_launch(head_mix_kernel<T, TW>, dim3(rows), dim3(threads), 0, s, (const T*)src, lds, (const TW*)talk, (T*)out, ldo, token_seq, heads, kvh, hd, vd)
+    if (dtype == BRAID_F32 && talk_dtype == BRAID_F32) BRAID_MIX(float, float);
+    else if (dtype == BRAID_BF16 && talk_dtype == BRAID_BF16) BRAID_MIX(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == BRAID_BF16 && talk_dtype == BRAID_F32) BRAID_MIX(__nv_bfloat16, float);
+    else BRAID_REFUSE("head_mix: unknown dtype codes rows=%d talk=%d", dtype, talk_dtype);
+#undef BRAID_MIX
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ bias + xIELU
+// out[r, j] = f(z[r, j] + b[j]) for j < J, with the two-piece activation
+//     f(t) = softplus(p) t^2 + t / 2                           t > 0
+//     f(t) = (1/2 + softplus(q)) (exp(t) - 1 - t) + t / 2      t <= 0
+// whose two numbers (p, q) are stored with the layer (`pq`).  Columns J .. ldo of out are written as 1, 0, 0, ...: the
+// product that reads out then adds its own bias as the weight column that meets the 1.  float32 arithmetic.
+template <typename T, typename TW>
+__global__ void bias_xielu_kernel(const T* __restrict__ z, long long ldz, const TW* __restrict__ b, const TW* __restrict__ pq,
+                                  T* __restrict__ out, long long ldo, int J, int cols) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float p = to_f32(pq[0]), q = to_f32(pq[1]);
+    const float ap = fmaxf(p, 0.f) + log1pf(expf(-fabsf(p)));
+    const float aq = 0.5f + fmaxf(q, 0.f) + log1pf(expf(-fabsf(q)));
+    const T* zr = z + (size_t)row * ldz;
+    T* o = out + (size_t)row * ldo;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        float y;
+        if (j < J) {
+            const float t = to_f32(zr[j]) + to_f32(b[j]);
+            y = t > 0.f ? fmaf(ap * t, t, 0.5f * t) : fmaf(aq, expm1f(t) - t, 0.5f * t);
+        } else {
+            y = j == J ? 1.f : 0.f;
+        }
+        o[j] = from_f32<T>(y);
+    }
+}
+
+extern "C" int braid_bias_xielu(const void* z, long long ldz, const void* b, const void* pq, int w_dtype, void* out,
+                                long long ldo, int dtype, int rows, int J, int cols, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (J <= 0 || cols < J || cols > ldo) BRAID_REFUSE("bias_xielu: %d numbers a row, %d columns written, rows of %lld", J, cols, ldo);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = cols >= 1024 ? 256 : 128;
+#define BRAID_XI(T, TW) braid_launch(bias_xielu_kernel<T, TW>, dim3(rows), dim3(threads), 0, s, (const T*)z, ldz, (const TW*)b, (const TW*)pq, (T*)out, ldo, J, cols)
+    if (dtype == BRAID_F32 && w_dtype == BRAID_F32) BRAID_XI(float, float);
+    else if (dtype == BRAID_BF16 && w_dtype == BRAID_BF16) BRAID_XI(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == BRAID_BF16 && w_dtype == BRAID_F32) BRAID_XI(__nv_bfloat16, float);
+    else BRAID_REFUSE("bias_xielu: unknown dtype codes rows=%d weights=%d", dtype, w_dtype);
+#undef BRAID_XI
+    BRAID_LAUNCH_CHECK();
+}

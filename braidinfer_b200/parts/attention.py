@@ -23,9 +23,18 @@ Options that other designs use, each off unless named:
     q_temp          {"coef", "every"}: the query at position p is multiplied by
                     1 + coef * ln(floor((p + 1) / every) + 1), a temperature that sharpens long contexts
     value_dim       the size of a value head where it differs from head_dim
-The last three are for heads that are not rotated (position encoding "none"): one kernel norms, scales and
+    keep_first      with a window: a sequence's first keep_first positions stay visible at any distance (key j is seen from
+                    position p iff j <= p and (p - j < window or j < keep_first)); they keep their true positions
+    head_scale      a stored tensor of num_heads numbers: head h's scores are multiplied by head_scale[h] (float32)
+    talk            a stored [num_heads, num_heads] tensor T that mixes the heads' probabilities after the softmax,
+                    p'_h = sum_g T[h, g] p_g; head h applies p'_h to the values of its own kv head.  The mix is linear, so
+                    every head's own probabilities are applied to the values of every kv head (the attention kernels'
+                    `value_heads`) and the results are mixed afterwards, out_h = sum_g T[h, g] O[g, kv(h)] (`head_mix`)
+unit_qk_eps, q_temp and value_dim without rotation are for heads that are not rotated (position encoding "none"): one kernel norms, scales and
 stores.  Keys, values and queries are then padded with zeros to one head size that the attention kernels take
-(max(head_dim, value_dim), rounded up to 16), which changes no score and no result.
+(max(head_dim, value_dim), rounded up to 16), which changes no score and no result.  Rotated heads whose value
+size differs from head_dim (or whose size is no multiple of 16) get the same padding from rows of zeros in the
+stacked projection, put there when the weights are loaded.
 """
 from __future__ import annotations
 
@@ -44,7 +53,7 @@ class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (int | None),
     position_encoding (PartSpec), and tensor names q_proj, k_proj, v_proj, o_proj; optional qk_norm
     ({"eps", "q_name", "k_name"}), value_from_key (bool), scale, sink (a score), out_mult, sink_name, head_gate,
-    unit_qk_eps, q_temp ({"coef", "every"}), value_dim."""
+    unit_qk_eps, q_temp ({"coef", "every"}), value_dim, keep_first, head_scale (a tensor name), talk (a tensor name)."""
 
     plain_output = True
 
@@ -59,7 +68,6 @@ class GQAAttention(Mixer):
         if self.nqh % self.nkh:
             raise ValueError(f"{self.nqh} query heads do not divide into {self.nkh} kv heads")
         pe: PartSpec = p["position_encoding"]
-        self.pe = POSITION_ENCODINGS.get(pe.kind)(pe.params, prefix, runtime)
         self.value_from_key = bool(p.get("value_from_key", False))
         self.vd = int(p.get("value_dim") or self.hd)
         self.unit_qk_eps = float(p["unit_qk_eps"]) if p.get("unit_qk_eps") is not None else None
@@ -76,6 +84,27 @@ class GQAAttention(Mixer):
             raise ValueError("gqa_attention: a gate a head rides in the stacked product, which the plain rotation kernels "
                              "take without further columns; it goes with head norms or with heads that are not rotated")
         self.hd_pad = -(-max(self.hd, self.vd) // 16) * 16 if self.prep else self.hd
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.head_scale_name = prefix + p["head_scale"] if p.get("head_scale") is not None else None
+        self.talk_name = prefix + p["talk"] if p.get("talk") is not None else None
+        self.head_scale = self.talk = None
+        # rotated heads with a value size of their own, or of a size the tensor-core kernels do not take: rows of zeros in
+        # the stacked projection pad every head to one size
+        self.pad_rows = (not self.prep and pe.kind != "none" and not self.value_from_key and p.get("qk_norm") is None
+                         and (self.vd != self.hd or (self.hd % 16 and (self.talk_name or self.keep_first))))
+        if self.pad_rows:
+            self.hd_pad = -(-max(self.hd, self.vd) // 16) * 16
+        if self.vd != self.hd and not (self.prep or self.pad_rows):
+            raise ValueError("gqa_attention: a value size of its own goes with plainly rotated heads or with heads without rotation")
+        if self.keep_first and not self.window:
+            raise ValueError("gqa_attention: keep_first goes with a window")
+        if self.talk_name and (gated or p.get("sink") is not None or p.get("sink_name") is not None):
+            raise ValueError("gqa_attention: the mix of the heads' probabilities is built for an ordinary softmax without "
+                             "sink or gate")
+        pe_params = dict(pe.params)
+        if self.pad_rows:
+            pe_params["head_dim"] = self.hd_pad          # the rotation still turns the first rope_dim numbers of a head
+        self.pe = POSITION_ENCODINGS.get(pe.kind)(pe_params, prefix, runtime)
         if self.prep and (pe.kind != "none" or self.value_from_key or p.get("qk_norm") is not None):
             raise ValueError("gqa_attention: unit norms, a query temperature and a value size of its own are for heads "
                              "without rotation, weighted head norms or keys as values")
@@ -114,6 +143,10 @@ class GQAAttention(Mixer):
             d[self.qk_norm[2]] = TensorSpec((self.hd,), init="one_plus_normal")
         if self.sink_name:
             d[self.sink_name] = TensorSpec((self.nqh,), std=1.0)
+        if self.head_scale_name:
+            d[self.head_scale_name] = TensorSpec((self.nqh,), init="one_plus_normal", std=0.1)
+        if self.talk_name:
+            d[self.talk_name] = TensorSpec((self.nqh, self.nqh), std=0.3)
         return d
 
     def load(self, tensors) -> None:
@@ -122,8 +155,22 @@ class GQAAttention(Mixer):
         pad = -w.shape[0] % 8            # rows of zeros, so that a row of the stacked result starts on 16 bytes
         if pad and (self.qk_norm or self.value_from_key):     # (the plain rotation kernels take rows without padding)
             self.qkv.weight = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)]).contiguous()
+        if self.pad_rows:
+            # every head of q, k and v padded with rows of zeros to hd_pad: no score and no result changes
+            w, D = self.qkv.weight, self.hd_pad
+            parts, at = [], 0
+            for heads, size in ((self.nqh, self.hd), (self.nkh, self.hd), (self.nkh, self.vd)):
+                blk = w[at:at + heads * size].view(heads, size, w.shape[1])
+                at += heads * size
+                parts.append(torch.cat([blk, torch.zeros((heads, D - size, w.shape[1]), dtype=w.dtype, device=w.device)], 1)
+                             .reshape(heads * D, w.shape[1]))
+            self.qkv.weight = torch.cat(parts).contiguous()
         self.o.load(tensors)
         self.pe.load(tensors)
+        if self.head_scale_name:
+            self.head_scale = tensors[self.head_scale_name].float().contiguous()   # scores are float32 in every run
+        if self.talk_name:
+            self.talk = tensors[self.talk_name].contiguous()
         if self.qk_norm:
             self.q_norm_w, self.k_norm_w = tensors[self.qk_norm[1]], tensors[self.qk_norm[2]]
         if self.sink_name:
@@ -131,7 +178,7 @@ class GQAAttention(Mixer):
 
     def cache_request(self) -> Optional[CacheRequest]:
         kind = "window" if self.window else "full"
-        return CacheRequest(kind, self.nkh, self.hd_pad, self.window)
+        return CacheRequest(kind, self.nkh, self.hd_pad, self.window, keep_first=self.keep_first if self.window else 0)
 
     def takes_row_scale(self) -> bool:
         return self.qkv.takes_row_scale()
@@ -151,8 +198,20 @@ class GQAAttention(Mixer):
         else:
             self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
         rows = x.shape[0]
-        out = rt.empty(rows, self.nqh * self.hd)
-        self._attend(qkv, out, ctx, cache, self.hd, gate)
+        D = self.hd_pad
+        if self.talk is not None:
+            # every head's probabilities over the values of every kv head, then the mix of the heads
+            wide = rt.empty(rows, self.nqh * self.nkh * D)
+            self._attend(qkv, wide, ctx, cache, D, value_heads=self.nkh)
+            out = rt.empty(rows, self.nqh * self.vd)
+            rt.kernels.head_mix(wide, self.talk, out, ctx.token_seq, self.nqh, self.nkh, D, self.vd)
+            return self._project(out, residual, ctx)
+        out = rt.empty(rows, self.nqh * D)
+        self._attend(qkv, out, ctx, cache, D, gate)
+        if D != self.vd:
+            y = rt.empty(rows, self.nqh * self.vd)
+            rt.kernels.head_gate(out, None, y, self.nqh, D, self.vd)
+            out = y
         return self._project(out, residual, ctx)
 
     def _project(self, out, residual, ctx):
@@ -179,7 +238,7 @@ class GQAAttention(Mixer):
             out = y
         return self._project(out, residual, ctx)
 
-    def _attend(self, qkv, out, ctx, cache, hd, gate=None) -> None:
+    def _attend(self, qkv, out, ctx, cache, hd, gate=None, value_heads: int = 1) -> None:
         """Pick the attention kernel for this step.  float32 runs, and runs that ask for
         the plain kernels, use the one-warp-per-query kernel for everything.  bfloat16
         runs use the tcgen05 kernel for prompts (head sizes 64 and 128; "mma" as the
@@ -188,10 +247,12 @@ class GQAAttention(Mixer):
         so that a handful of sequences still fills the machine."""
         K = self.rt.kernels
         plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(hd))
-        if plain:
+        extras = bool(self.keep_first) or self.head_scale is not None or value_heads > 1
+        if plain or extras:
             K.attn_simple(qkv, out, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
                           self.nqh, self.nkh, hd, cache.page_size, self.window, self.scale, sink=self.sink,
-                          head_sinks=self.head_sinks, head_gate=gate, out_scale=self.out_mult)
+                          head_sinks=self.head_sinks, head_gate=gate, out_scale=self.out_mult,
+                          keep_first=self.keep_first, head_scale=self.head_scale, value_heads=value_heads)
             return
         few = ctx.max_q_len <= 8
         if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(hd):

@@ -6,7 +6,15 @@ kernels/megakernel_ops.hip:1474-1545 gate/up with silu as x / (1 + exp(-x)),
 tensor-core path the activation is its epilogue.
 
 "clamped_glu": down( g * sigmoid(alpha * g) * (u + 1) ) with g = min(gate x, limit) and u = clamp(up x, -limit, limit):
-a gated unit whose two branches are bounded before they meet, and whose linear branch is offset by one."""
+a gated unit whose two branches are bounded before they meet, and whose linear branch is offset by one.
+
+"biased_mlp": down( f(up x + b_up) ) + b_down, one hidden layer with biases and no gate.  Its activation f is the
+two-piece xIELU with two stored numbers (p, q) a layer:
+    f(t) = softplus(p) t^2 + t / 2                           t > 0
+    f(t) = (1/2 + softplus(q)) (exp(t) - 1 - t) + t / 2      t <= 0
+(Huang, Schlag: "Deriving Activation Functions Using Integration", 2024, in the form with both numbers under a
+softplus).  The up bias and the activation are one float32 kernel; the down bias is one more column of the down
+matrix that meets a column of ones which that kernel writes, so it costs no launch."""
 from __future__ import annotations
 
 from typing import Dict
@@ -85,6 +93,60 @@ class ClampedGLU(FeedForward):
         gu = self.gate_up.forward(x)                           # [rows, gate | up]
         act = self.rt.empty(x.shape[0], self.inter)
         self.rt.kernels.glu_clamp(gu, act, self.limit, self.alpha)
+        if residual is None:
+            return self.down.forward(act, out_dtype=torch.float32)
+        return self.down.forward(act, residual=residual, defer_to=ctx)
+
+
+@FEED_FORWARDS.register("biased_mlp")
+class BiasedMLP(FeedForward):
+    """params: hidden_size, intermediate_size, activation ("xielu"), tensor names up_proj, up_bias, down_proj, down_bias,
+    act (the activation's two numbers)."""
+
+    plain_output = True
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        if p.get("activation", "xielu") != "xielu":
+            raise ValueError(f"biased_mlp: activation {p.get('activation')!r} is not built (xielu)")
+        self.inter_pad = -(-(self.inter + 1) // 8) * 8          # the ones column, and rows that start on 16 bytes
+        self.up = Linear(runtime, [prefix + p.get("up_proj", "mlp.up")], [self.inter], self.hidden)
+        self.down_name = prefix + p.get("down_proj", "mlp.down")
+        self.up_bias_name = prefix + p.get("up_bias", "mlp.up.b")
+        self.down_bias_name = prefix + p.get("down_bias", "mlp.down.b")
+        self.act_name = prefix + p.get("act", "mlp.act")
+        self.down = Linear(runtime, [self.down_name], [self.hidden], self.inter_pad)
+        self.up_bias = self.act_pq = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        d = dict(self.up.tensor_specs())
+        d[self.up_bias_name] = TensorSpec((self.inter,))
+        d[self.down_name] = TensorSpec((self.hidden, self.inter))
+        d[self.down_bias_name] = TensorSpec((self.hidden,))
+        d[self.act_name] = TensorSpec((2,), std=0.5)
+        return d
+
+    def load(self, tensors) -> None:
+        self.up.load(tensors)
+        w, b = tensors[self.down_name], tensors[self.down_bias_name]
+        if w.dtype != b.dtype:
+            w, b = w.float(), b.float()
+        pad = torch.zeros((self.hidden, self.inter_pad - self.inter - 1), dtype=w.dtype, device=w.device)
+        self.down.share(torch.cat([w, b.view(-1, 1), pad], dim=1).contiguous())      # [hidden, ff | bias | zeros]
+        self.up_bias, self.act_pq = tensors[self.up_bias_name], tensors[self.act_name]
+        if self.up_bias.dtype != self.act_pq.dtype:
+            self.up_bias, self.act_pq = self.up_bias.float(), self.act_pq.float()
+
+    def takes_row_scale(self) -> bool:
+        return self.up.takes_row_scale()
+
+    def forward(self, x, residual, ctx):
+        z = self.up.forward(x, in_scale=ctx.take_row_scale(x) if ctx is not None else None)
+        act = self.rt.empty(x.shape[0], self.inter_pad)
+        self.rt.kernels.bias_xielu(z, self.up_bias, self.act_pq, act, self.inter)
         if residual is None:
             return self.down.forward(act, out_dtype=torch.float32)
         return self.down.forward(act, residual=residual, defer_to=ctx)

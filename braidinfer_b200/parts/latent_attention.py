@@ -18,6 +18,12 @@ output is Wuv_h applied to the attended latent (`gemm_heads` again, with the gat
 and Wuv are used as stored; per-head transposes are made once at load, no product of weights is formed.
 
 A constant factor on the mixer's output (`out_mult`, a model's residual multiplier) rides on the gate.
+
+Options for other designs: the rotation may pair neighbours (2i, 2i + 1) instead of halves (the position encoding's
+`pairing`); `window` limits a query to the last `window` positions, itself included; `shared_kv` makes a layer
+without a down-projection of its own: it reads the latent and the rotated key part that an earlier layer cached
+(the schedule's `cache_of`), with its own queries, Wuk, Wuv, window and output; `cache_window` widens what the
+cache keeps beyond the layer's own window, for readers with a longer one.
 """
 from __future__ import annotations
 
@@ -35,8 +41,8 @@ class LatentAttention(Mixer):
     """params: hidden_size, num_heads, dim (unrotated query/key numbers a head), rot_dim (rotated ones),
     vdim (value size a head), kv_rank, scale (on the scores), eps (of the latent's RMS norm), window
     (int | None), out_mult (default 1), gated (default True), position_encoding (a PartSpec of kind "rope"
-    with head_dim = rot_dim: its rope_dim leading numbers of the rotated part turn), and the tensor names
-    q, dkv, dkv_norm, uk, uv, g, o (under the prefix)."""
+    with head_dim = rot_dim: its rope_dim leading numbers of the rotated part turn), shared_kv (default False),
+    cache_window (default: window), and the tensor names q, dkv, dkv_norm, uk, uv, g, o (under the prefix)."""
 
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
@@ -54,13 +60,21 @@ class LatentAttention(Mixer):
         self.gated = bool(p.get("gated", True))
         pe: PartSpec = p["position_encoding"]
         self.pe = POSITION_ENCODINGS.get(pe.kind)(pe.params, prefix, runtime)
-        if self.pe.head_dim != self.rot or getattr(self.pe, "pairing", "half") != "half":
-            raise ValueError("latent_attention rotates the rot_dim part of queries and the shared key part, "
-                             "element i with element i + rope_dim / 2")
+        if self.pe.head_dim != self.rot or getattr(self.pe, "amplitude", 1.0) != 1.0:
+            raise ValueError("latent_attention rotates the rot_dim part of queries and the shared key part, without a "
+                             "factor on sine and cosine")
+        self.adjacent = getattr(self.pe, "pairing", "half") == "adjacent"
+        self.shared_kv = bool(p.get("shared_kv", False))
+        self.cache_window = p.get("cache_window") or self.window
+        if self.window and self.cache_window < self.window:
+            raise ValueError("latent_attention: the cache must keep at least the layer's own window")
         self.q_cols = self.heads * (self.dim + self.rot)
         self.D = self.rank + self.rot
-        names = [prefix + p.get("q", "mix.q"), prefix + p.get("dkv", "mix.dkv")]
-        outs = [self.q_cols, self.D]
+        names, outs = [prefix + p.get("q", "mix.q")], [self.q_cols]
+        if not self.shared_kv:
+            names.append(prefix + p.get("dkv", "mix.dkv"))
+            outs.append(self.D)
+        self.gate_col = sum(outs)
         if self.gated:
             names.append(prefix + p.get("g", "mix.g"))
             outs.append(self.heads)
@@ -73,7 +87,8 @@ class LatentAttention(Mixer):
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         d = dict(self.proj.tensor_specs())
-        d[self.norm_name] = TensorSpec((self.rank,), init="one_plus_normal")
+        if not self.shared_kv:
+            d[self.norm_name] = TensorSpec((self.rank,), init="one_plus_normal")
         d[self.uk_name] = TensorSpec((self.heads * self.dim, self.rank))
         d[self.uv_name] = TensorSpec((self.heads * self.vdim, self.rank))
         d.update(self.o.tensor_specs())
@@ -88,13 +103,13 @@ class LatentAttention(Mixer):
             self.proj.weight = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)]).contiguous()
         self.o.load(tensors)
         self.pe.load(tensors)
-        self.norm_w = tensors[self.norm_name]
+        self.norm_w = tensors[self.norm_name] if not self.shared_kv else None
         # [heads, kv_rank, dim]: head h's matrix that carries q_u into the latent space, [out, in]
         self.uk_t = tensors[self.uk_name].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.uv = tensors[self.uv_name].view(self.heads, self.vdim, self.rank).contiguous()
 
     def cache_request(self) -> Optional[CacheRequest]:
-        return CacheRequest("window" if self.window else "full", 1, self.D, self.window, planes=1)
+        return CacheRequest("window" if self.window else "full", 1, self.D, self.cache_window if self.window else None, planes=1)
 
     def forward(self, x, residual, ctx, cache, state):
         if cache is None:
@@ -104,16 +119,19 @@ class LatentAttention(Mixer):
         proj = self.proj.forward(x)                                   # [rows, q | c' kr' | gate | padding]
         q_lat = self.rt.empty(rows, self.heads, self.D)
         writable = not cache.read_only
+        if self.shared_kv and writable:
+            raise RuntimeError("latent_attention: a layer without a down-projection reads another layer's cache (cache_of)")
         K.latent_prep(proj, self.q_cols, self.norm_w, self.pe.inv_freq, ctx.positions, ctx.token_seq,
                       cache.page_table if writable else None, cache.storage if writable else None, q_lat,
-                      self.heads, self.dim, self.rot, self.rank, self.pe.rope_dim, cache.page_size, self.eps)
+                      self.heads, self.dim, self.rot, self.rank, self.pe.rope_dim, cache.page_size, self.eps,
+                      adjacent=self.adjacent)
         q_u = proj[:, :self.q_cols].view(rows, self.heads, self.dim + self.rot)[:, :, :self.dim]
         tc = self.rt.gemm_backend == "auto"
         K.gemm_heads(q_u, self.uk_t, q_lat[:, :, :self.rank], tensor_cores=tc)
         o_lat = self.rt.empty(rows, self.heads, self.rank)
         self._attend(q_lat, o_lat, ctx, cache)
         out = self.rt.empty(rows, self.heads * self.vdim)
-        gate = proj[:, self.q_cols + self.D:self.q_cols + self.D + self.heads] if self.gated else None
+        gate = proj[:, self.gate_col:self.gate_col + self.heads] if self.gated else None
         if gate is None and self.out_mult != 1.0:
             raise RuntimeError("latent_attention: an output factor needs the gate's epilogue")
         K.gemm_heads(o_lat, self.uv, out.view(rows, self.heads, self.vdim), gate=gate, mult=self.out_mult, tensor_cores=tc)

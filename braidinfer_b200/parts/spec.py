@@ -99,13 +99,15 @@ class CacheRequest:
     kind "full": keys and values of every past token; "window": of the last
     `window` tokens only.  Layers whose requests are equal share one group of
     storage.  `planes` is how many vectors of `head_dim` a token and kv head keep:
-    2 for a key and a value, 1 where one vector serves as both (a latent).
+    2 for a key and a value, 1 where one vector serves as both (a latent).  `keep_first` (kind "window"): the
+    sequence's first positions stay beside the window, for mixers whose queries see them at any distance.
     """
     kind: str
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    keep_first: int = 0
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.planes)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.planes, self.keep_first)
