@@ -462,21 +462,33 @@ class Kernels:
     def attn_mma_supports(head_dim: int) -> bool:
         return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
-    def attn_mma_library(self, head_dim: int):
-        """The attention library for one head size, compiled at first use."""
-        lib = self._attn_libs.get(head_dim)
+    @staticmethod
+    def attn_value_heads_a_launch(head_dim: int, value_heads: int) -> int:
+        """How many kv heads' values a query head reads in one launch of the mma.sync kernel: as many as its
+        float32 accumulators hold (value heads x head_dim up to 256), a divisor of `value_heads`."""
+        return max(d for d in range(1, value_heads + 1) if value_heads % d == 0 and (d == 1 or d * head_dim <= 256))
+
+    def attn_mma_library(self, head_dim: int, value_heads: int = 1):
+        """The attention library for one head size (and, `value_heads` > 1, for a query head that reads the values
+        of that many kv heads a launch), compiled at first use."""
+        key = head_dim if value_heads == 1 else (head_dim, value_heads)
+        lib = self._attn_libs.get(key)
         if lib is None:
             if not self.attn_mma_supports(head_dim):
                 raise KernelError(f"the tensor-core attention takes head sizes in steps of 16 up to 256, not {head_dim}")
-            lib = ctypes.CDLL(str(build.attention_library(head_dim, verbose=self._verbose)))
+            lib = ctypes.CDLL(str(build.attention_library(head_dim, verbose=self._verbose, value_heads=value_heads)))
             lib.braid_last_error.restype = c_char_p
             lib.braid_attn_mma.restype = c_int
             lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 13 + [c_float, c_int, c_float, c_float, c_void_p, c_void_p,
-                                           c_longlong, c_void_p, c_void_p]
+                                           c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
             lib.braid_attn_mma_partial_floats.restype = c_longlong
             lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
-            lib.braid_attn_tc_supported.restype = c_int
-            lib.has_tc = bool(lib.braid_attn_tc_supported())
+            if lib.braid_attn_mma_value_heads() != value_heads:
+                raise KernelError("the attention library was built for another number of value heads")
+            lib.has_tc = False
+            if value_heads == 1:
+                lib.braid_attn_tc_supported.restype = c_int
+                lib.has_tc = bool(lib.braid_attn_tc_supported())
             if lib.has_tc:
                 lib.braid_attn_tc.restype = c_int
                 lib.braid_attn_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong] + [c_void_p] * 4 + [c_int] * 10 + \
@@ -484,7 +496,7 @@ class Kernels:
             lib.braid_attn_mma_decode_slots.restype = c_int
             lib.braid_attn_mma_decode_slots.argtypes = [c_int]
             lib.decode_slots = lib.braid_attn_mma_decode_slots(1)     # CTAs of the few-token kernel held at once
-            self._attn_libs[head_dim] = lib
+            self._attn_libs[key] = lib
         return lib
 
     @staticmethod
@@ -521,41 +533,50 @@ class Kernels:
         if rc != 0:
             raise KernelError(f"attn_tc: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
-    def attn_decode_slots(self, head_dim: int) -> int:
-        return self.attn_mma_library(head_dim).decode_slots
+    def attn_decode_slots(self, head_dim: int, value_heads: int = 1) -> int:
+        vh = self.attn_value_heads_a_launch(head_dim, value_heads) if value_heads > 1 else 1
+        return self.attn_mma_library(head_dim, vh).decode_slots
 
     def attn_mma(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                  q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,
                  n_seqs: int, max_q_len: int, nqh: int, nkh: int, hd: int, window: Optional[int], scale: float,
                  n_splits: int = 1, few_tokens: bool = False, sink: Optional[float] = None,
                  out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
-                 head_gate: Optional[torch.Tensor] = None) -> None:
+                 head_gate: Optional[torch.Tensor] = None, keep_first: int = 0,
+                 head_scale: Optional[torch.Tensor] = None, value_heads: int = 1) -> None:
         """bfloat16 attention over the cache on the tensor cores; `n_splits` > 1 slices the
         context (for steps of few tokens) and merges the slices in a second kernel.  `sink`, `head_sinks`,
-        `out_scale` and `head_gate` as in `attn_simple` (the sink is counted once, where the slices merge)."""
-        lib = self.attn_mma_library(hd)
-        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype)
+        `out_scale`, `head_gate`, `keep_first`, `head_scale` and `value_heads` as in `attn_simple` (the sink is counted
+        once, where the slices merge; the values of all kv heads take one launch, or several where the accumulators
+        do not hold them all)."""
+        vh = self.attn_value_heads_a_launch(hd, value_heads) if value_heads > 1 else 1
+        lib = self.attn_mma_library(hd, vh)
+        self._check_head_extras(head_sinks, head_gate, nqh, out.dtype, head_scale)
         self._check_pages(cache)
         rows = out.shape[0]
+        if value_heads > 1 and (value_heads != nkh or out.shape[1] < nqh * nkh * hd):
+            raise KernelError("attn_mma: a head reads the values of its own kv head or of all, and the result holds them")
         partial = None
         if n_splits > 1:
-            need = lib.braid_attn_mma_partial_floats(rows, nqh, n_splits)
+            need = lib.braid_attn_mma_partial_floats(rows, nqh * value_heads, n_splits)
             if self._attn_partial is None or self._attn_partial.numel() < need:
                 self._attn_partial = torch.empty(max(need, 1 << 22), dtype=torch.float32, device="cuda")
                 self.workspace_generation += 1
             partial = self._attn_partial
             self.launches += 1
-        self.launches += 1
-        rc = lib.braid_attn_mma(q.data_ptr(), out.data_ptr(), _ptr(partial), cache.data_ptr(), page_table.data_ptr(),
-                                q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(),
-                                q.stride(0), out.stride(0), rows, n_seqs, max_q_len, nqh, nkh, hd,
-                                page_table.shape[1], cache.shape[0], int(window or 0), n_splits,
-                                1 if few_tokens else 0, float(scale), int(sink is not None), float(sink or 0.0),
-                                float(out_scale), _ptr(head_sinks), _ptr(head_gate),
-                                head_gate.stride(0) if head_gate is not None else 0,
-                                self._error_flag.data_ptr() + 16, self._stream())
-        if rc != 0:
-            raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
+        for vh0 in range(0, value_heads, vh):
+            self.launches += 1
+            rc = lib.braid_attn_mma(q.data_ptr(), out.data_ptr(), _ptr(partial), cache.data_ptr(), page_table.data_ptr(),
+                                    q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(),
+                                    q.stride(0), out.stride(0), rows, n_seqs, max_q_len, nqh, nkh, hd,
+                                    page_table.shape[1], cache.shape[0], int(window or 0), n_splits,
+                                    1 if few_tokens else 0, float(scale), int(sink is not None), float(sink or 0.0),
+                                    float(out_scale), _ptr(head_sinks), _ptr(head_gate),
+                                    head_gate.stride(0) if head_gate is not None else 0, int(keep_first or 0),
+                                    _ptr(head_scale), vh0, value_heads if value_heads > 1 else 0,
+                                    self._error_flag.data_ptr() + 16, self._stream())
+            if rc != 0:
+                raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
     # ------------------------------------------------------------------ element-wise kernels of other models
     def dyt(self, x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,

@@ -12,7 +12,12 @@
 // braid_attn_combine to merge: that is how a single decoded token fills the machine.
 //
 // Visibility is the one rule of the whole library: key j is visible to the query at
-// position p iff j <= p and (window == 0 or p - j < window).
+// position p iff j <= p and (window == 0 or p - j < window); with keep_first > 0 the sequence's first
+// keep_first positions stay visible beyond the window (their tiles are walked before the window's).
+// head_scale is a factor a head on the scores.  Compiled with -DBRAID_VH=<n> (default 1) and called with
+// vh_total > 0, every query head applies its probabilities to the values of kv heads vh0 .. vh0 + n - 1 as well as
+// sharing the keys of its own kv head, and writes the results at virtual heads head * vh_total + vh0 + c: what a
+// mix of the heads' probabilities after the softmax needs (pointwise.cu, head_mix).
 //
 // Replaces the reference's op_attn_paged, one 256-thread block per query head walking
 // the context token by token (kernels/megakernel_ops.hip:2150-2343).
@@ -22,6 +27,10 @@
 #error "compile with -DBRAID_HD=<head_dim>"
 #endif
 static_assert(BRAID_HD % 16 == 0 && BRAID_HD >= 16 && BRAID_HD <= 256, "head_dim must be a multiple of 16 in [16, 256]");
+#ifndef BRAID_VH
+#define BRAID_VH 1
+#endif
+static_assert(BRAID_VH >= 1 && BRAID_VH * BRAID_HD <= 512, "value heads a launch times head_dim must fit the accumulators");
 
 #include "page.h"
 #define PAGE BRAID_PAGE_SIZE
@@ -46,6 +55,9 @@ struct AttnMmaArgs {
     const float* head_sinks;     // [nqh] float32 natural-log scores: a sink a head (learned) instead of the one score; or null
     const __nv_bfloat16* head_gate;  // [rows, gate_stride]: head h's result is multiplied by sigmoid(head_gate[row, h]); or null
     long long gate_stride;
+    int keep_first;              // with a window: the first positions of a sequence stay visible
+    const float* head_scale;     // [nqh] float32: a factor a head on the scores; or null
+    int vh0, vh_total;           // vh_total > 0: the values of kv heads vh0 .. vh0 + VH - 1, results at virtual heads
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -75,11 +87,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD, int NW, int BN, int ST>
 struct AttnCfg {
     static_assert(PAGE % BN == 0, "a key tile must not straddle a page");
+    static constexpr int VH = BRAID_VH;                   // value tiles beside a key tile
     static constexpr int BM = 16 * NW;
     static constexpr int ROW = HD * 2 + 16;               // bytes per padded shared-memory row
     static constexpr int Q_BYTES = BM * ROW;
     static constexpr int TILE_BYTES = BN * ROW;           // one K or V tile
-    static constexpr int SMEM = Q_BYTES + ST * 2 * TILE_BYTES;
+    static constexpr int STAGE_BYTES = (1 + VH) * TILE_BYTES;
+    static constexpr int SMEM = Q_BYTES + ST * STAGE_BYTES;
 };
 
 template <int HD, int NW, int BN, int ST>
@@ -111,13 +125,17 @@ attn_mma_kernel(AttnMmaArgs a) {
     const int n_tok = min(tpc, q_len - tok0);
     const int pos_min = kv_before + tok0, pos_max = pos_min + n_tok - 1;
     const int k_lo = (a.window > 0 && pos_min - a.window + 1 > 0) ? pos_min - a.window + 1 : 0;
-    int t_lo = k_lo / BN, t_hi = pos_max / BN + 1;
+    // the tiles this CTA walks: those of the kept first positions that the window has left behind, then the window's
+    const int t_win = k_lo / BN;
+    const int n_first = min((a.keep_first + BN - 1) / BN, t_win);
+    int i_lo = 0, i_hi = n_first + pos_max / BN + 1 - t_win;
     if (a.n_splits > 1) {
-        const int per = (t_hi - t_lo + a.n_splits - 1) / a.n_splits;
-        t_lo = t_lo + split * per;
-        t_hi = min(t_hi, t_lo + per);
+        const int per = (i_hi - i_lo + a.n_splits - 1) / a.n_splits;
+        i_lo = i_lo + split * per;
+        i_hi = min(i_hi, i_lo + per);
     }
-    const int n_tiles = max(0, t_hi - t_lo);
+    const int n_tiles = max(0, i_hi - i_lo);
+    auto tile_of = [&](int i) { return i < n_first ? i : t_win + (i - n_first); };
     const int* table = a.page_table + (size_t)seq * a.table_cols;
     const int head0 = kvh * g + hchunk * hpc;              // first query head of this CTA
     const int n_heads = min(hpc, g - hchunk * hpc);
@@ -133,13 +151,16 @@ attn_mma_kernel(AttnMmaArgs a) {
         }
         const int off = key0 - block * PAGE;
         const __nv_bfloat16* kbase = a.cache + (((size_t)page * 2) * a.nkh + kvh) * PAGE * HD + (size_t)off * HD;
-        const __nv_bfloat16* vbase = kbase + (size_t)a.nkh * PAGE * HD;
-        uint8_t* dk = sKV + stage * 2 * C::TILE_BYTES;
+        // the values: of this kv head, or (vh_total > 0) of kv heads vh0 .. vh0 + VH - 1
+        const __nv_bfloat16* vbase = kbase + (size_t)(a.nkh + (a.vh_total > 0 ? a.vh0 - kvh : 0)) * PAGE * HD;
+        uint8_t* dk = sKV + stage * C::STAGE_BYTES;
         uint8_t* dv = dk + C::TILE_BYTES;
         for (int i = tid; i < BN * CH; i += NW * 32) {
             const int r = i / CH, c = i - r * CH;
             cp_async16(dk + r * C::ROW + c * 16, kbase + (size_t)r * HD + c * 8);
-            cp_async16(dv + r * C::ROW + c * 16, vbase + (size_t)r * HD + c * 8);
+#pragma unroll
+            for (int v = 0; v < C::VH; ++v)
+                cp_async16(dv + v * C::TILE_BYTES + r * C::ROW + c * 16, vbase + (size_t)v * PAGE * HD + (size_t)r * HD + c * 8);
         }
     };
     // the first tiles of the ring; those that hold only positions cached before this step
@@ -147,8 +168,8 @@ attn_mma_kernel(AttnMmaArgs a) {
     bool early[ST];                                      // every stage of the ring is free at the start
 #pragma unroll
     for (int s = 0; s < ST; ++s) {
-        early[s] = s < n_tiles && (t_lo + s + 1) * BN <= kv_before;
-        if (early[s]) load_tile(t_lo + s, s);
+        early[s] = s < n_tiles && (tile_of(i_lo + s) + 1) * BN <= kv_before;
+        if (early[s]) load_tile(tile_of(i_lo + s), s);
     }
     pdl_wait();
 
@@ -156,7 +177,7 @@ attn_mma_kernel(AttnMmaArgs a) {
     // for the queries, next, then runs beside theirs
 #pragma unroll
     for (int s = 0; s < ST; ++s) {
-        if (s < n_tiles && !early[s]) load_tile(t_lo + s, s);
+        if (s < n_tiles && !early[s]) load_tile(tile_of(i_lo + s), s);
         cp_async_commit();                               // one group a stage, as the loop below counts them
     }
 
@@ -174,29 +195,32 @@ attn_mma_kernel(AttnMmaArgs a) {
     // per-thread rows: r0 = lane / 4 and r0 + 8 of this warp's 16
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
     int pos_a = -1, pos_b = -1;                            // -1: the row sees nothing
+    float sc_a = a.scale_log2, sc_b = a.scale_log2;        // the factor on the row's scores
     {
         const int ta = row_a / hpc, ha = row_a - ta * hpc;
         const int tb = row_b / hpc, hb = row_b - tb * hpc;
-        if (ta < n_tok && ha < n_heads) pos_a = pos_min + ta;
-        if (tb < n_tok && hb < n_heads) pos_b = pos_min + tb;
+        if (ta < n_tok && ha < n_heads) { pos_a = pos_min + ta; if (a.head_scale) sc_a *= a.head_scale[head0 + ha]; }
+        if (tb < n_tok && hb < n_heads) { pos_b = pos_min + tb; if (a.head_scale) sc_b *= a.head_scale[head0 + hb]; }
     }
     const int lo_a = (a.window > 0) ? pos_a - a.window + 1 : 0;
     const int lo_b = (a.window > 0) ? pos_b - a.window + 1 : 0;
 
-    float o[HD / 8][4];
+    float o[C::VH][HD / 8][4];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    for (int v = 0; v < C::VH; ++v)
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) { o[v][i][0] = o[v][i][1] = o[v][i][2] = o[v][i][3] = 0.f; }
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     for (int it = 0; it < n_tiles; ++it) {
         if (it > 0) {                                    // the stage that tile it - 1 has left takes tile it + ST - 1
             const int pre = it + ST - 1;
-            if (pre < n_tiles) load_tile(t_lo + pre, pre % ST);
+            if (pre < n_tiles) load_tile(tile_of(i_lo + pre), pre % ST);
             cp_async_commit();
         }
         cp_async_wait<ST - 1>();
         __syncthreads();
-        const uint8_t* sK = sKV + (it % ST) * 2 * C::TILE_BYTES;
+        const uint8_t* sK = sKV + (it % ST) * C::STAGE_BYTES;
         const uint8_t* sV = sK + C::TILE_BYTES;
 
         // ---- S = Q K^T
@@ -217,17 +241,17 @@ attn_mma_kernel(AttnMmaArgs a) {
         }
 
         // ---- mask, online softmax
-        const int key0 = (t_lo + it) * BN + (lane & 3) * 2;
+        const int key0 = tile_of(i_lo + it) * BN + (lane & 3) * 2;
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = key0 + nb * 8 + e;
-                const bool va = (j <= pos_a) && (j >= lo_a);
-                const bool vb = (j <= pos_b) && (j >= lo_b);
-                s[nb][e] = va ? s[nb][e] * a.scale_log2 : -INFINITY;
-                s[nb][2 + e] = vb ? s[nb][2 + e] * a.scale_log2 : -INFINITY;
+                const bool va = (j <= pos_a) && (j >= lo_a || j < a.keep_first);
+                const bool vb = (j <= pos_b) && (j >= lo_b || j < a.keep_first);
+                s[nb][e] = va ? s[nb][e] * sc_a : -INFINITY;
+                s[nb][2 + e] = vb ? s[nb][2 + e] * sc_b : -INFINITY;
                 mx_a = fmaxf(mx_a, s[nb][e]);
                 mx_b = fmaxf(mx_b, s[nb][2 + e]);
             }
@@ -251,7 +275,9 @@ attn_mma_kernel(AttnMmaArgs a) {
         l_a = l_a * corr_a + sum_a;
         l_b = l_b * corr_b + sum_b;
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+        for (int v = 0; v < C::VH; ++v)
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) { o[v][i][0] *= corr_a; o[v][i][1] *= corr_a; o[v][i][2] *= corr_b; o[v][i][3] *= corr_b; }
 
         // ---- O += P V
 #pragma unroll
@@ -261,12 +287,14 @@ attn_mma_kernel(AttnMmaArgs a) {
             const uint32_t p2 = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
             const uint32_t p3 = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
 #pragma unroll
-            for (int db = 0; db < HD / 16; ++db) {
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(b0, b1, b2, b3, sV + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * C::ROW + (db * 16 + (lane >> 4) * 8) * 2);
-                mma_bf16(o[db * 2], p0, p1, p2, p3, b0, b1);
-                mma_bf16(o[db * 2 + 1], p0, p1, p2, p3, b2, b3);
-            }
+            for (int v = 0; v < C::VH; ++v)
+#pragma unroll
+                for (int db = 0; db < HD / 16; ++db) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_trans(b0, b1, b2, b3, sV + v * C::TILE_BYTES + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * C::ROW + (db * 16 + (lane >> 4) * 8) * 2);
+                    mma_bf16(o[v][db * 2], p0, p1, p2, p3, b0, b1);
+                    mma_bf16(o[v][db * 2 + 1], p0, p1, p2, p3, b2, b3);
+                }
         }
         __syncthreads();
     }
@@ -286,6 +314,26 @@ attn_mma_kernel(AttnMmaArgs a) {
         const int head = head0 + hl;
         float l = half ? l_b : l_a;
         const float m = half ? m_b : m_a;
+        if (a.vh_total > 0) {                            // virtual heads: no sink and no gate here
+            const float inv = a.out_scale / l;
+#pragma unroll
+            for (int v = 0; v < C::VH; ++v) {
+                const size_t vhead = (size_t)head * a.vh_total + a.vh0 + v;
+                if (a.n_splits == 1) {
+                    __nv_bfloat16* dst = a.out + grow * a.out_row_stride + vhead * HD + (lane & 3) * 2;
+#pragma unroll
+                    for (int i = 0; i < HD / 8; ++i)
+                        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[v][i][half * 2] * inv, o[v][i][half * 2 + 1] * inv);
+                } else {
+                    float* dst = a.partial + ((grow * a.nqh * a.vh_total + vhead) * a.n_splits + split) * (HD + 2);
+                    if ((lane & 3) == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+                    for (int i = 0; i < HD / 8; ++i)
+                        *reinterpret_cast<float2*>(dst + 2 + i * 8 + (lane & 3) * 2) = make_float2(o[v][i][half * 2], o[v][i][half * 2 + 1]);
+                }
+            }
+            continue;
+        }
         if (a.n_splits == 1) {
             float corr = 1.f;
             if (a.has_sink) {                            // the sink joins as one more score, with no value
@@ -299,13 +347,13 @@ attn_mma_kernel(AttnMmaArgs a) {
             __nv_bfloat16* dst = a.out + grow * a.out_row_stride + (size_t)head * HD + (lane & 3) * 2;
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i)
-                *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][half * 2] * inv, o[i][half * 2 + 1] * inv);
+                *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[0][i][half * 2] * inv, o[0][i][half * 2 + 1] * inv);
         } else {
             float* dst = a.partial + ((grow * a.nqh + head) * a.n_splits + split) * (HD + 2);
             if ((lane & 3) == 0) { dst[0] = m; dst[1] = l; }
 #pragma unroll
             for (int i = 0; i < HD / 8; ++i)
-                *reinterpret_cast<float2*>(dst + 2 + i * 8 + (lane & 3) * 2) = make_float2(o[i][half * 2], o[i][half * 2 + 1]);
+                *reinterpret_cast<float2*>(dst + 2 + i * 8 + (lane & 3) * 2) = make_float2(o[0][i][half * 2], o[0][i][half * 2 + 1]);
         }
     }
 }
@@ -388,6 +436,7 @@ static int launch_attn(const AttnMmaArgs& a, int n_seqs, int max_q_len, cudaStre
 }
 
 extern "C" int braid_attn_mma_head_dim(void) { return BRAID_HD; }
+extern "C" int braid_attn_mma_value_heads(void) { return BRAID_VH; }
 
 // Floats of scratch that n_splits > 1 needs.
 extern "C" long long braid_attn_mma_partial_floats(int rows, int nqh, int n_splits) {
@@ -414,9 +463,16 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
                               int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
                               int nqh, int nkh, int hd, int table_cols, int num_pages, int window, int n_splits, int kind,
                               float scale, int has_sink, float sink_score, float out_scale, const float* head_sinks,
-                              const void* head_gate, long long gate_stride, int* error_flag, void* stream) {
+                              const void* head_gate, long long gate_stride, int keep_first, const float* head_scale,
+                              int vh0, int vh_total, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
     if (head_sinks) has_sink = 1;
+    if (vh_total < 0 || (vh_total > 0 && (vh_total != nkh || vh0 < 0 || vh0 + BRAID_VH > vh_total)))
+        BRAID_REFUSE("attn_mma: value heads %d .. %d of %d do not fit %d kv heads", vh0, vh0 + BRAID_VH - 1, vh_total, nkh);
+    if (vh_total == 0 && BRAID_VH != 1) BRAID_REFUSE("attn_mma: this library was compiled for %d value heads a query head", BRAID_VH);
+    if (vh_total > 0 && (has_sink || head_gate)) BRAID_REFUSE("attn_mma: values of every kv head go with an ordinary softmax without sink or gate");
+    if (keep_first < 0) BRAID_REFUSE("attn_mma: keep_first=%d must not be negative", keep_first);
+    if (window <= 0) keep_first = 0;
     // a gate a head rides on the last kernel that touches a row: the merge of the slices, or the attention itself
     const __nv_bfloat16* gate_here = n_splits > 1 ? nullptr : (const __nv_bfloat16*)head_gate;
     if (!error_flag) BRAID_REFUSE("attn_mma: error_flag is required");
@@ -430,15 +486,17 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (float*)partial, (const __nv_bfloat16*)cache, page_table,
                   q_start, q_len, kv_before, q_row_stride, out_row_stride, nqh, nkh, table_cols, window, n_splits,
                   scale * 1.4426950408889634f, num_pages, error_flag, has_sink, sink_score * 1.4426950408889634f, out_scale,
-                  head_sinks, gate_here, gate_stride};
+                  head_sinks, gate_here, gate_stride, keep_first, head_scale, vh0, vh_total};
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
     else rc = launch_attn<1, 32, 3>(a, n_seqs, max_q_len, s);
     if (rc) return rc;
-    if (n_splits > 1) {
-        dim3 grid(rows, nqh);
-        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits, has_sink, sink_score * 1.4426950408889634f, out_scale, head_sinks, (const __nv_bfloat16*)head_gate, gate_stride);
+    // the slices merge once every value head of a row is there: with the launch of the last ones
+    if (n_splits > 1 && (vh_total == 0 || vh0 + BRAID_VH == vh_total)) {
+        const int vheads = vh_total > 0 ? nqh * vh_total : nqh;
+        dim3 grid(rows, vheads);
+        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, vheads, n_splits, has_sink, sink_score * 1.4426950408889634f, out_scale, head_sinks, (const __nv_bfloat16*)head_gate, gate_stride);
         BRAID_LAUNCH_CHECK();
     }
     return BRAID_OK;
@@ -485,5 +543,6 @@ extern "C" int braid_attn_mma_noalloc(const void* q, void* out, const void* cach
     }
     return braid_attn_mma(q, out, n_splits > 1 ? g_noalloc_ptr[dev] : nullptr, cache, page_table, q_start, q_len,
                           kv_before, token_seq, q_row_stride, out_row_stride, rows, n_seqs, max_q_len, nqh, nkh, hd,
-                          table_cols, num_pages, window, n_splits, kind, scale, 0, 0.f, 1.f, nullptr, nullptr, 0, error_flag, stream);
+                          table_cols, num_pages, window, n_splits, kind, scale, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, nullptr, 0, 0,
+                          error_flag, stream);
 }

@@ -181,8 +181,12 @@ def latent_attention_library(rank: int, rot: int, verbose: bool = True) -> Path:
                          defines=[f"-DBRAID_LAT_RANK={rank}", f"-DBRAID_LAT_ROT={rot}"], verbose=verbose)
 
 
-def attention_library(head_dim: int, verbose: bool = True) -> Path:
+def attention_library(head_dim: int, verbose: bool = True, value_heads: int = 1) -> Path:
     """The tensor-core attention kernels compiled for one head size (what a model needs
-    is compiled when the model is first built)."""
+    is compiled when the model is first built).  `value_heads` > 1: the mma.sync kernel alone, compiled so that a
+    query head reads the values of that many kv heads a launch."""
+    if value_heads > 1:
+        return build_library(f"braidinfer_attn_hd{head_dim}_vh{value_heads}", ["errors.cu", "attn_mma.cu"],
+                             defines=[f"-DBRAID_HD={head_dim}", f"-DBRAID_VH={value_heads}"], verbose=verbose)
     return build_library(f"braidinfer_attn_hd{head_dim}", ["errors.cu", "attn_mma.cu", "attn_tc.cu"],
                          defines=[f"-DBRAID_HD={head_dim}"], verbose=verbose)

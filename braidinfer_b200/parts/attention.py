@@ -78,7 +78,7 @@ class GQAAttention(Mixer):
         # heads that are normed without weights, scaled by position or of two sizes go through the kernel that
         # pads them to one size
         gated = p.get("head_gate") is not None
-        self.prep = (self.unit_qk_eps is not None or self.q_temp is not None or self.vd != self.hd
+        self.prep = (self.unit_qk_eps is not None or self.q_temp is not None or (self.vd != self.hd and pe.kind == "none")
                      or (gated and pe.kind == "none"))
         if gated and not self.prep and not (p.get("qk_norm") is not None or self.value_from_key):
             raise ValueError("gqa_attention: a gate a head rides in the stacked product, which the plain rotation kernels "
@@ -248,14 +248,14 @@ class GQAAttention(Mixer):
         K = self.rt.kernels
         plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(hd))
         extras = bool(self.keep_first) or self.head_scale is not None or value_heads > 1
-        if plain or extras:
+        if plain:
             K.attn_simple(qkv, out, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
                           self.nqh, self.nkh, hd, cache.page_size, self.window, self.scale, sink=self.sink,
                           head_sinks=self.head_sinks, head_gate=gate, out_scale=self.out_mult,
                           keep_first=self.keep_first, head_scale=self.head_scale, value_heads=value_heads)
             return
         few = ctx.max_q_len <= 8
-        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(hd):
+        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(hd) and not extras:
             K.attn_tc(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before,
                       ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, hd, self.window, self.scale, sink=self.sink,
                       head_sinks=self.head_sinks, head_gate=gate, out_scale=self.out_mult)
@@ -264,11 +264,12 @@ class GQAAttention(Mixer):
         if few:
             g = self.nqh // self.nkh
             ctas = ctx.n_seqs * self.nkh * -(-g // 16)
-            span = min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len
+            span = min(ctx.max_kv_len, self.window + self.keep_first) if self.window else ctx.max_kv_len
             tiles = max(1, -(-span // 32))
             # one wave of CTAs over the device, and at least four key tiles a slice
-            n_splits = max(1, min(K.attn_decode_slots(hd) // ctas, tiles // 4, 64))
+            n_splits = max(1, min(K.attn_decode_slots(hd, value_heads) // ctas, tiles // 4, 64))
         K.attn_mma(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before, ctx.token_seq,
                    ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, hd, self.window, self.scale,
                    n_splits=n_splits, few_tokens=few, sink=self.sink, head_sinks=self.head_sinks, head_gate=gate,
-                   out_scale=self.out_mult)
+                   out_scale=self.out_mult, keep_first=self.keep_first, head_scale=self.head_scale,
+                   value_heads=value_heads)
