@@ -1385,6 +1385,218 @@ def birepel_kernels(z, T, B, C, timed, frac):
     return res
 
 
+# ------------------------------------------------------------------ the Ludazen decoder beside the Bidinex one
+def ludazen_config(z):
+    """Attention and latent layers in turn at the sizes of `BIDINEX_SIZES`: the latent layers are the other model's
+    (behind a window, without gates), the second of them reads the first one's latent; the attention layers have its
+    head count, a kv head for four heads, heads as large as a latent head's query, a window of 1,024 with four kept
+    tokens; the experts are the other model's (chosen by sigmoid scores, beside a shared one of an expert's size), the
+    dense feed-forward is as wide as the experts a token uses."""
+    hd = 128 if z["dim"] + z["rot"] > 64 else 64
+    att = {"heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+           "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+           "mask": {"size": 1024, "keep_first": 4}}
+    lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "rot": {"base": 10000.0, "dims": z["rot"]},
+           "vdim": z["vdim"], "kv_rank": z["rank"], "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["ff"]}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    layers, owner = [], None
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "attention", "mixer": att, "mlp": dense if i % 4 == 0 else moe})
+        else:
+            layers.append({"type": "latent_attention", "mixer": dict(lat, **({"kv_from": owner} if owner is not None else {})),
+                           "mlp": moe if owner is None else dense})
+            owner = i if owner is None else owner
+    return {"architecture": "Ludazen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def run_ludazen(args):
+    """`--ludazen`: prompt and decode throughput of the Ludazen decoder at sizes like a real model's layers (random
+    weights, four layers), beside the Bidinex decoder of equal size (the closest model here: latent attention and a
+    mixture of experts), and the new kernels and kernel options one by one beside the like kernels that the other
+    models run, with their fractions of the measured peaks.  Prints one JSON line of its own; the default run and
+    its line are untouched."""
+    import torch
+    from braidinfer_b200.engine import Engine
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps=5, warm=2, graph=False):
+        for _ in range(warm):
+            fn()
+        run = fn
+        if graph:
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            run = gr.replay
+            run()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / 1e3)
+        return statistics.median(ts)
+
+    def frac(seconds, flops, nbytes):
+        return max(flops / (pk["bf16_tflops"] * 1e12), nbytes / (pk["hbm_gbs"] * 1e9)) / seconds
+
+    T, B, C = args.prompt_len, args.batch, args.context
+    sizes = [n for n in BIDINEX_SIZES if not args.sizes or n in args.sizes.split(",")]
+    out = {"metric": "ludazen_beside_bidinex_decoder", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic, random weights",
+           "prompt_len": T, "decode_batch": B, "decode_context": C, "peaks": pk, "l2": "flushed between timed calls", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name in sizes:
+            z = BIDINEX_SIZES[name]
+            row = {}
+            for label, cfg in (("ludazen", ludazen_config(z)), ("bidinex", bidinex_config(z))):
+                eng = Engine.from_random(cfg, 1, dtype="bfloat16", on_device=True, max_tokens=max(B * (C + 192), T + 64),
+                                         max_slots=B, verbose=False)
+                g = torch.Generator().manual_seed(0)
+                prompt = torch.randint(0, z["vocab"], (T,), generator=g).tolist()
+
+                def prefill():
+                    s = eng.open()
+                    eng.step([(s, prompt)], want="last")
+                    eng.close(s)
+                tp = timed(prefill, reps=3, warm=2)
+                prompts = [torch.randint(0, z["vocab"], (C,), generator=g).tolist() for _ in range(B)]
+                secs, ctx0, launches = device_timed_decode(eng, eng.kernels, prompts, args.steps, max(args.warmup, 3))
+                eng.check()
+                row[label] = {"prefill_tokens_per_s": round(T / tp), "prefill_ms": round(tp * 1e3, 3),
+                              "decode_tokens_per_s": round(B * args.steps / secs), "decode_ms_per_step": round(secs / args.steps * 1e3, 4),
+                              "weight_gb": round(eng.weight_bytes / 1e9, 3), "cache_mb": round(eng.cache.nbytes() / 1e6, 1),
+                              "launches_per_decode_step": launches // args.steps}
+                del eng
+                torch.cuda.empty_cache()
+            row["kernels"] = ludazen_kernels(z, T, B, C, timed, frac)
+            out["sizes"][name] = row
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
+def ludazen_kernels(z, T, B, C, timed, frac):
+    """The new kernels and options alone, each beside the like kernel of another model: seconds, and the fraction of
+    the measured peak that its algorithmic FLOPs or bytes (whichever bounds it) reach.  The attention whose heads'
+    probabilities are mixed is charged with the FLOPs of the design (scores and values once a head); what its kernels
+    compute beyond that (the values of every kv head a query head) shows as a lower fraction."""
+    import torch
+    from types import SimpleNamespace
+    from braidinfer_b200.cache import PAGE_SIZE
+    from braidinfer_b200.csrc.api import get_kernels
+    K = get_kernels(verbose=False)
+    dev, bf = "cuda", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)        # noqa: E731
+    H, Wd, E, top, ff, R, rot = z["heads"], z["width"], z["experts"], z["top"], z["ff"], z["rank"], z["rot"]
+    hd = 128 if z["dim"] + z["rot"] > 64 else 64
+    nkh, win, keep, D = max(1, H // 4), 1024, 4, R + rot
+    res = {}
+
+    def paged(n_seqs, length, planes, heads, dim):
+        blocks = -(-length // PAGE_SIZE)
+        cache = torch.randn(n_seqs * blocks, planes, heads, PAGE_SIZE, dim, device=dev, dtype=bf) * 0.5
+        table = torch.arange(n_seqs * blocks, dtype=torch.int32, device=dev).view(n_seqs, blocks)
+        return cache, table
+
+    def steps_of(n_seqs, each, before):
+        return SimpleNamespace(q_start=i32([i * each for i in range(n_seqs)]), q_len=i32([each] * n_seqs),
+                               kv_before=i32([before] * n_seqs),
+                               token_seq=torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each))
+
+    temp, talk = torch.rand(H, device=dev) + 0.5, (torch.randn(H, H, device=dev) * 0.3).to(bf)
+    # ---- attention over a prompt and of decoded tokens: heads mixed after the softmax (every query head over the values
+    # of every kv head, then the mix) beside the plain windowed attention of the same heads
+    for what, n_seqs, each, before in (("prompt_attention", 1, T, 0), ("decode_attention", B, 1, C - 1)):
+        st = steps_of(n_seqs, each, before)
+        rows = n_seqs * each
+        cache, table = paged(n_seqs, before + each, 2, nkh, hd)
+        q = torch.randn(rows, (H + 2 * nkh) * hd, device=dev, dtype=bf) * 0.3
+        wide = torch.empty(rows, H * nkh * hd, device=dev, dtype=bf)
+        o = torch.empty(rows, H * hd, device=dev, dtype=bf)
+        few = each <= 8
+        seen = sum(min(p + 1, win) + min(keep, max(p + 1 - win, 0)) for p in range(before, before + each)) * n_seqs
+        fl = 2 * 2 * H * hd * seen
+        nbytes = n_seqs * min(before + each, win + keep) * nkh * 2 * hd * 2
+        sp = sp1 = 1
+        if few:
+            ctas = n_seqs * nkh * -(-(H // nkh) // 16)
+            tiles = max(1, (min(before + each, win + keep)) // 32)
+            sp = max(1, min(K.attn_decode_slots(hd, nkh) // (ctas * (nkh // K.attn_value_heads_a_launch(hd, nkh))), tiles // 4, 64))
+            sp1 = max(1, min(K.attn_decode_slots(hd) // ctas, tiles // 4, 64))
+
+        def mixed():
+            K.attn_mma(q, wide, cache, table, st.q_start, st.q_len, st.kv_before, st.token_seq, n_seqs, each, H, nkh, hd, win,
+                       hd ** -0.5, n_splits=sp, few_tokens=few, keep_first=keep, head_scale=temp, value_heads=nkh)
+            K.head_mix(wide, talk, o, st.token_seq, H, nkh, hd, hd)
+        t1 = timed(mixed, graph=True)
+        t1a = timed(lambda: K.head_mix(wide, talk, o, st.token_seq, H, nkh, hd, hd), graph=True)
+        t2 = timed(lambda: K.attn_mma(q, o, cache, table, st.q_start, st.q_len, st.kv_before, st.token_seq, n_seqs, each, H, nkh, hd,
+                                      win, hd ** -0.5, n_splits=sp1, few_tokens=few), graph=True)
+        res[what] = {"mixed_heads_ms": round(t1 * 1e3, 4), "mixed_heads_frac": round(frac(t1, fl, nbytes), 3),
+                     "of_which_mix_ms": round(t1a * 1e3, 4),
+                     "mix_frac": round(frac(t1a, 0, rows * (H * nkh * hd + H * hd) * 2), 3),
+                     "plain_window_ms": round(t2 * 1e3, 4), "plain_window_frac": round(frac(t2, fl, nbytes), 3),
+                     "groups_of_value_heads": nkh // K.attn_value_heads_a_launch(hd, nkh), "slices": sp}
+    # ---- latent attention behind a window beside the same kernel over the whole context (the Bidinex layer)
+    for what, n_seqs, each, before in (("prompt_latent_attention", 1, T, 0), ("decode_latent_attention", B, 1, C - 1)):
+        st = steps_of(n_seqs, each, before)
+        rows = n_seqs * each
+        cache, table = paged(n_seqs, before + each, 1, 1, D)
+        q = torch.randn(rows, H, D, device=dev, dtype=bf) * 0.3
+        o = torch.empty(rows, H, R, device=dev, dtype=bf)
+        row = {}
+        for label, w in (("window", win), ("whole", None)):
+            span = min(before + each, w) if w else before + each
+            sp = 1
+            if each <= 8:
+                sp = max(1, min(296 // K.attn_latent_ctas(R, rot, n_seqs, each, H), (span // 32) // 4, 32))
+            t = timed(lambda: K.attn_latent_mma(q, o, cache, table, st.q_start, st.q_len, st.kv_before, st.token_seq, n_seqs, each, R, w,
+                                                0.1, n_splits=sp), graph=True)
+            seen = sum(min(p + 1, w) if w else p + 1 for p in range(before, before + each)) * n_seqs
+            row.update({label + "_ms": round(t * 1e3, 4), label + "_frac": round(frac(t, 2 * H * (D + R) * seen, n_seqs * span * D * 2), 3)})
+        res[what] = row
+    # ---- the experts' first products with the weight on their input beside the same without, and routing
+    for what, rows in (("prompt_experts", T), ("decode_experts", B)):
+        x = torch.randn(rows, Wd, device=dev, dtype=bf) * 0.3
+        wg, wu = [torch.randn(E, ff, Wd, device=dev, dtype=bf) * 0.02 for _ in range(2)]
+        logits = torch.randn(rows, E, device=dev)
+        idx = torch.empty(rows, top, dtype=torch.int32, device=dev)
+        wgt = torch.empty(rows, top, dtype=torch.float32, device=dev)
+        tr1 = timed(lambda: K.moe_route(logits, idx, wgt, 1, 1, sigmoid=True), graph=True)
+        tr2 = timed(lambda: K.moe_route(logits, idx, wgt, 1, 1), graph=True)
+        tile = 16 if rows * top <= 16 * E else 64
+        plan = K.moe_plan(idx, torch.zeros(rows, dtype=torch.int32, device=dev), E, tile)
+        act = torch.empty(plan[4] * tile, ff, device=dev, dtype=bf)
+        t1 = timed(lambda: K.moe_gemm_mma(x, wg, wu, act, plan, top, tile, in_wgt=wgt), graph=True)
+        t2 = timed(lambda: K.moe_gemm_mma(x, wg, wu, act, plan, top, tile), graph=True)
+        used = int(torch.unique(idx).numel())
+        fl1, by1 = 2 * rows * top * 2 * ff * Wd, used * 2 * ff * Wd * 2
+        res[what] = {"weighted_input_ms": round(t1 * 1e3, 4), "weighted_input_frac": round(frac(t1, fl1, by1), 3),
+                     "weighted_output_ms": round(t2 * 1e3, 4), "weighted_output_frac": round(frac(t2, fl1, by1), 3),
+                     "route_sigmoid_ms": round(tr1 * 1e3, 4), "route_softmax_ms": round(tr2 * 1e3, 4), "experts_used": used, "tile": tile}
+        del wg, wu
+    # ---- bias + two-piece activation (with the ones column) beside the gated unit's activation kernel
+    I = top * ff
+    for what, rows in (("prompt_activation", T), ("decode_activation", B)):
+        zz = torch.randn(rows, 2 * I, device=dev, dtype=bf)
+        bias, pq = torch.randn(I, device=dev, dtype=bf), torch.tensor([0.3, -0.2], device=dev, dtype=bf)
+        a1 = torch.empty(rows, I + 8, device=dev, dtype=bf)
+        a2 = torch.empty(rows, I, device=dev, dtype=bf)
+        t1 = timed(lambda: K.bias_xielu(zz[:, :I], bias, pq, a1, I), graph=True)
+        t2 = timed(lambda: K.act_mul(zz, a2, "silu"), graph=True)
+        res[what] = {"bias_xielu_ms": round(t1 * 1e3, 4), "bias_xielu_frac": round(frac(t1, 0, rows * I * 4), 3),
+                     "gated_silu_ms": round(t2 * 1e3, 4), "gated_silu_frac": round(frac(t2, 0, rows * I * 6), 3)}
+    return res
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
@@ -1426,7 +1638,10 @@ def main() -> int:
     ap.add_argument("--birepel", action="store_true",
                     help="another measurement: the Birepel decoder at sizes like a real model's layers beside the Loduzen "
                          "decoder of equal size, and its kernels one by one; prints its own line (see run_birepel)")
-    ap.add_argument("--sizes", default="", help="with --bidinex / --loduzen / --birepel: names of the sizes, with commas (default: all)")
+    ap.add_argument("--ludazen", action="store_true",
+                    help="another measurement: the Ludazen decoder at sizes like a real model's layers beside the Bidinex "
+                         "decoder of equal size, and its kernels one by one; prints its own line (see run_ludazen)")
+    ap.add_argument("--sizes", default="", help="with --bidinex / --loduzen / --birepel / --ludazen: names of the sizes, with commas (default: all)")
     ap.add_argument("--prompt-len", type=int, default=2048, help="with --bidinex: tokens of the timed prompt")
     ap.add_argument("--context", type=int, default=2048, help="with --bidinex: context of the timed decode steps")
     args = ap.parse_args()
@@ -1441,6 +1656,8 @@ def main() -> int:
         return run_loduzen(args)
     if args.birepel:
         return run_birepel(args)
+    if args.ludazen:
+        return run_ludazen(args)
     if args.sweep:
         return run_sweep(args)
     if args.prompt_timeline:

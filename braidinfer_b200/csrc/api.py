@@ -547,8 +547,8 @@ class Kernels:
         """bfloat16 attention over the cache on the tensor cores; `n_splits` > 1 slices the
         context (for steps of few tokens) and merges the slices in a second kernel.  `sink`, `head_sinks`,
         `out_scale`, `head_gate`, `keep_first`, `head_scale` and `value_heads` as in `attn_simple` (the sink is counted
-        once, where the slices merge; the values of all kv heads take one launch, or several where the accumulators
-        do not hold them all)."""
+        once, where the slices merge; where the accumulators do not hold the values of all kv heads, groups of them
+        go to CTAs of their own)."""
         vh = self.attn_value_heads_a_launch(hd, value_heads) if value_heads > 1 else 1
         lib = self.attn_mma_library(hd, vh)
         self._check_head_extras(head_sinks, head_gate, nqh, out.dtype, head_scale)
@@ -564,7 +564,7 @@ class Kernels:
                 self.workspace_generation += 1
             partial = self._attn_partial
             self.launches += 1
-        for vh0 in range(0, value_heads, vh):
+        for vh0 in (0,):                       # one launch: the groups of value heads are part of its grid
             self.launches += 1
             rc = lib.braid_attn_mma(q.data_ptr(), out.data_ptr(), _ptr(partial), cache.data_ptr(), page_table.data_ptr(),
                                     q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(),

@@ -15,9 +15,10 @@
 // position p iff j <= p and (window == 0 or p - j < window); with keep_first > 0 the sequence's first
 // keep_first positions stay visible beyond the window (their tiles are walked before the window's).
 // head_scale is a factor a head on the scores.  Compiled with -DBRAID_VH=<n> (default 1) and called with
-// vh_total > 0, every query head applies its probabilities to the values of kv heads vh0 .. vh0 + n - 1 as well as
-// sharing the keys of its own kv head, and writes the results at virtual heads head * vh_total + vh0 + c: what a
-// mix of the heads' probabilities after the softmax needs (pointwise.cu, head_mix).
+// vh_total > 0, every query head applies its probabilities to the values of every kv head as well as
+// sharing the keys of its own kv head, n value heads a CTA (the grid grows by vh_total / n), and writes the results at
+// virtual heads head * vh_total + value head: what a mix of the heads' probabilities after the softmax needs
+// (pointwise.cu, head_mix).
 //
 // Replaces the reference's op_attn_paged, one 256-thread block per query head walking
 // the context token by token (kernels/megakernel_ops.hip:2150-2343).
@@ -57,7 +58,7 @@ struct AttnMmaArgs {
     long long gate_stride;
     int keep_first;              // with a window: the first positions of a sequence stay visible
     const float* head_scale;     // [nqh] float32: a factor a head on the scores; or null
-    int vh0, vh_total;           // vh_total > 0: the values of kv heads vh0 .. vh0 + VH - 1, results at virtual heads
+    int vh0, vh_total;           // vh_total > 0: the values of kv heads vh0 .. vh_total - 1, VH of them a CTA, results at virtual heads
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -115,7 +116,10 @@ attn_mma_kernel(AttnMmaArgs a) {
     // CTAs start in the order x, y, z: every kv head and sequence of the last token tile first, then of
     // the tile before: late tokens see the most keys, so the longest CTAs start first
     const int seq = blockIdx.y;
-    const int kvh = blockIdx.x / hchunks, hchunk = blockIdx.x - kvh * hchunks;
+    // blockIdx.x: (group of VH value heads, kv head, chunk of its query heads); the groups exist only with vh_total > 0
+    const int vgroup = blockIdx.x / (a.nkh * hchunks), bx = blockIdx.x - vgroup * (a.nkh * hchunks);
+    const int kvh = bx / hchunks, hchunk = bx - kvh * hchunks;
+    const int vh0 = a.vh0 + vgroup * C::VH;
     const int unit = gridDim.z - 1 - blockIdx.z;
     const int tile = unit / a.n_splits, split = unit - tile * a.n_splits;
     const int q_len = a.q_len[seq];
@@ -152,7 +156,7 @@ attn_mma_kernel(AttnMmaArgs a) {
         const int off = key0 - block * PAGE;
         const __nv_bfloat16* kbase = a.cache + (((size_t)page * 2) * a.nkh + kvh) * PAGE * HD + (size_t)off * HD;
         // the values: of this kv head, or (vh_total > 0) of kv heads vh0 .. vh0 + VH - 1
-        const __nv_bfloat16* vbase = kbase + (size_t)(a.nkh + (a.vh_total > 0 ? a.vh0 - kvh : 0)) * PAGE * HD;
+        const __nv_bfloat16* vbase = kbase + (size_t)(a.nkh + (a.vh_total > 0 ? vh0 - kvh : 0)) * PAGE * HD;
         uint8_t* dk = sKV + stage * C::STAGE_BYTES;
         uint8_t* dv = dk + C::TILE_BYTES;
         for (int i = tid; i < BN * CH; i += NW * 32) {
@@ -318,7 +322,7 @@ attn_mma_kernel(AttnMmaArgs a) {
             const float inv = a.out_scale / l;
 #pragma unroll
             for (int v = 0; v < C::VH; ++v) {
-                const size_t vhead = (size_t)head * a.vh_total + a.vh0 + v;
+                const size_t vhead = (size_t)head * a.vh_total + vh0 + v;
                 if (a.n_splits == 1) {
                     __nv_bfloat16* dst = a.out + grow * a.out_row_stride + vhead * HD + (lane & 3) * 2;
 #pragma unroll
@@ -430,7 +434,8 @@ static int launch_attn(const AttnMmaArgs& a, int n_seqs, int max_q_len, cudaStre
     const long long gx = (long long)((max_q_len + tpc - 1) / tpc) * a.n_splits;
     if (gx > 65535 || (long long)a.nkh * hchunks > 0x7fffffffLL || n_seqs > 65535)
         BRAID_REFUSE("attn_mma: the step exceeds the grid limits (%lld tiles, %d heads, %d sequences)", gx, a.nkh * hchunks, n_seqs);
-    dim3 grid(a.nkh * hchunks, n_seqs, (unsigned)gx);
+    const int vgroups = a.vh_total > 0 ? (a.vh_total - a.vh0) / BRAID_VH : 1;
+    dim3 grid(a.nkh * hchunks * vgroups, n_seqs, (unsigned)gx);
     braid_launch(attn_mma_kernel<BRAID_HD, NW, BN, ST>, dim3(grid), dim3(NW * 32), C::SMEM, s, a);
     BRAID_LAUNCH_CHECK();
 }
@@ -467,7 +472,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
                               int vh0, int vh_total, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
     if (head_sinks) has_sink = 1;
-    if (vh_total < 0 || (vh_total > 0 && (vh_total != nkh || vh0 < 0 || vh0 + BRAID_VH > vh_total)))
+    if (vh_total < 0 || (vh_total > 0 && (vh_total != nkh || vh0 < 0 || vh0 + BRAID_VH > vh_total || (vh_total - vh0) % BRAID_VH)))
         BRAID_REFUSE("attn_mma: value heads %d .. %d of %d do not fit %d kv heads", vh0, vh0 + BRAID_VH - 1, vh_total, nkh);
     if (vh_total == 0 && BRAID_VH != 1) BRAID_REFUSE("attn_mma: this library was compiled for %d value heads a query head", BRAID_VH);
     if (vh_total > 0 && (has_sink || head_gate)) BRAID_REFUSE("attn_mma: values of every kv head go with an ordinary softmax without sink or gate");
@@ -489,11 +494,16 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
                   head_sinks, gate_here, gate_stride, keep_first, head_scale, vh0, vh_total};
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
+    // with several value tiles a key tile, tiles of 32 keys leave room for two CTAs an SM (registers and shared memory)
+#if BRAID_VH > 1
+    if (kind == 0) rc = launch_attn<4, 32, 3>(a, n_seqs, max_q_len, s);
+#else
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
+#endif
     else rc = launch_attn<1, 32, 3>(a, n_seqs, max_q_len, s);
     if (rc) return rc;
-    // the slices merge once every value head of a row is there: with the launch of the last ones
-    if (n_splits > 1 && (vh_total == 0 || vh0 + BRAID_VH == vh_total)) {
+    // the slices merge once every value head of a row is there
+    if (n_splits > 1) {
         const int vheads = vh_total > 0 ? nqh * vh_total : nqh;
         dim3 grid(rows, vheads);
         braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, vheads, n_splits, has_sink, sink_score * 1.4426950408889634f, out_scale, head_sinks, (const __nv_bfloat16*)head_gate, gate_stride);

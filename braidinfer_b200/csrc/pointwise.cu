@@ -167,24 +167,67 @@ extern "C" int braid_rmsnorm_add(float* h, const float* y, const void* w, int w_
 // src [rows, heads * kv_heads, hd] -> out [rows, heads, vd] (the first vd numbers of a head: heads may be padded).
 // The sum over g is float32, in the order of g.
 template <typename T, typename TW>
-__global__ void head_mix_kernel(const T* __restrict__ src, long long lds, const TW* __restrict__ talk, T* __restrict__ out,
-                                long long ldo, const int* __restrict__ token_seq, int heads, int kvh, int hd, int vd) {
+__global__ void __launch_bounds__(128)
+head_mix_kernel(const T* __restrict__ src, long long lds, const TW* __restrict__ talk, T* __restrict__ out,
+                long long ldo, const int* __restrict__ token_seq, int heads, int kvh, int hd, int vd) {
+    // one CTA a row and kv head c: the results of every head over c's values wait in shared memory, and the heads of
+    // c's group each take their mix of them
+    extern __shared__ float mix_slab[];                    // [heads][vd]
     pdl_trigger();
     pdl_wait();
-    const int row = blockIdx.x;
+    const int row = blockIdx.x, c = blockIdx.y;
     const bool padding = token_seq && token_seq[row] < 0;
     const int group = heads / kvh;
     const T* s = src + (size_t)row * lds;
     T* o = out + (size_t)row * ldo;
-    for (int i = threadIdx.x; i < heads * vd; i += blockDim.x) {
-        const int h = i / vd, d = i - h * vd;
-        float acc = 0.f;
-        if (!padding) {
-            const int c = h / group;
-            for (int g = 0; g < heads; ++g)
-                acc = fmaf(to_f32(talk[h * heads + g]), to_f32(s[((size_t)g * kvh + c) * hd + d]), acc);
+    // 16 bytes a thread where rows and heads allow it (bfloat16: eight numbers)
+    constexpr int VEC = 16 / sizeof(T);
+    const bool wide = sizeof(T) == 2 && hd % VEC == 0 && vd % VEC == 0 && lds % VEC == 0 && ldo % VEC == 0 &&
+                      (((uintptr_t)src | (uintptr_t)out) & 15) == 0;
+    if (!padding) {
+        if (wide) {
+            const int per = vd / VEC;
+            for (int i = threadIdx.x; i < heads * per; i += blockDim.x) {
+                const int g = i / per, d = (i - g * per) * VEC;
+                T raw[VEC];
+                *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(s + ((size_t)g * kvh + c) * hd + d);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) mix_slab[g * vd + d + e] = to_f32(raw[e]);
+            }
+        } else {
+            for (int i = threadIdx.x; i < heads * vd; i += blockDim.x) {
+                const int g = i / vd, d = i - g * vd;
+                mix_slab[i] = to_f32(s[((size_t)g * kvh + c) * hd + d]);
+            }
         }
-        o[i] = from_f32<T>(acc);
+    }
+    __syncthreads();
+    if (wide) {
+        const int per = vd / VEC;
+        for (int i = threadIdx.x; i < group * per; i += blockDim.x) {
+            const int h = c * group + i / per, d = (i % per) * VEC;
+            float acc[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+            if (!padding)
+                for (int g = 0; g < heads; ++g) {
+                    const float w = to_f32(talk[h * heads + g]);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w, mix_slab[g * vd + d + e], acc[e]);
+                }
+            T raw[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) raw[e] = from_f32<T>(acc[e]);
+            *reinterpret_cast<uint4*>(o + (size_t)h * vd + d) = *reinterpret_cast<const uint4*>(raw);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < group * vd; i += blockDim.x) {
+        const int h = c * group + i / vd, d = i % vd;
+        float acc = 0.f;
+        if (!padding)
+            for (int g = 0; g < heads; ++g) acc = fmaf(to_f32(talk[h * heads + g]), mix_slab[g * vd + d], acc);
+        o[(size_t)h * vd + d] = from_f32<T>(acc);
     }
 }
 
@@ -192,9 +235,19 @@ extern "C" int braid_head_mix(const void* src, long long lds, const void* talk, 
                               int dtype, const int* token_seq, int rows, int heads, int kvh, int hd, int vd, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (heads <= 0 || kvh <= 0 || heads % kvh || vd <= 0 || vd > hd) BRAID_REFUSE("head_mix: heads=%d kv heads=%d head size=%d value size=%d", heads, kvh, hd, vd);
+    const size_t smem = (size_t)heads * vd * sizeof(float);
+    if (smem > 200 * 1024) BRAID_REFUSE("head_mix: %d heads of %d values are more than one block's shared memory holds", heads, vd);
+    if (kvh > 65535) BRAID_REFUSE("head_mix: %d kv heads exceed the grid limit", kvh);
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = heads * vd >= 1024 ? 256 : 128;
-#define BRAID_MIX(T, TW) braid_launch(head_mix_kernel<T, TW>, dim3(rows), dim3(threads), 0, s, (const T*)src, lds, (const TW*)talk, (T*)out, ldo, token_seq, heads, kvh, hd, vd)
+#define BRAID_MIX(T, TW)                                                                                               \
+    do {                                                                                                               \
+        if (smem > 48 * 1024) {                                                                                        \
+            cudaError_t e_ = cudaFuncSetAttribute(head_mix_kernel<T, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e_ != cudaSuccess) BRAID_REFUSE("head_mix: shared memory: %s", cudaGetErrorString(e_));                 \
+        }                                                                                                              \
+        braid_launch(head_mix_kernel<T, TW>, dim3(rows, kvh), dim3(128), smem, s, (const T*)src, lds, (const TW*)talk, \
+                     (T*)out, ldo, token_seq, heads, kvh, hd, vd);                                                     \
+    } while (0)
     if (dtype == BRAID_F32 && talk_dtype == BRAID_F32) BRAID_MIX(float, float);
     else if (dtype == BRAID_BF16 && talk_dtype == BRAID_BF16) BRAID_MIX(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == BRAID_BF16 && talk_dtype == BRAID_F32) BRAID_MIX(__nv_bfloat16, float);
@@ -209,18 +262,20 @@ extern "C" int braid_head_mix(const void* src, long long lds, const void* talk, 
 //     f(t) = (1/2 + softplus(q)) (exp(t) - 1 - t) + t / 2      t <= 0
 // whose two numbers (p, q) are stored with the layer (`pq`).  Columns J .. ldo of out are written as 1, 0, 0, ...: the
 // product that reads out then adds its own bias as the weight column that meets the 1.  float32 arithmetic.
+#define XIELU_SPAN 1024
 template <typename T, typename TW>
 __global__ void bias_xielu_kernel(const T* __restrict__ z, long long ldz, const TW* __restrict__ b, const TW* __restrict__ pq,
                                   T* __restrict__ out, long long ldo, int J, int cols) {
     pdl_trigger();
     pdl_wait();
-    const int row = blockIdx.x;
+    const int row = blockIdx.x;                            // blockIdx.y: a span of XIELU_SPAN columns
     const float p = to_f32(pq[0]), q = to_f32(pq[1]);
     const float ap = fmaxf(p, 0.f) + log1pf(expf(-fabsf(p)));
     const float aq = 0.5f + fmaxf(q, 0.f) + log1pf(expf(-fabsf(q)));
     const T* zr = z + (size_t)row * ldz;
     T* o = out + (size_t)row * ldo;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    const int j_end = min(cols, (int)(blockIdx.y + 1) * XIELU_SPAN);
+    for (int j = blockIdx.y * XIELU_SPAN + threadIdx.x; j < j_end; j += blockDim.x) {
         float y;
         if (j < J) {
             const float t = to_f32(zr[j]) + to_f32(b[j]);
@@ -237,8 +292,8 @@ extern "C" int braid_bias_xielu(const void* z, long long ldz, const void* b, con
     if (rows <= 0) return BRAID_OK;
     if (J <= 0 || cols < J || cols > ldo) BRAID_REFUSE("bias_xielu: %d numbers a row, %d columns written, rows of %lld", J, cols, ldo);
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = cols >= 1024 ? 256 : 128;
-#define BRAID_XI(T, TW) braid_launch(bias_xielu_kernel<T, TW>, dim3(rows), dim3(threads), 0, s, (const T*)z, ldz, (const TW*)b, (const TW*)pq, (T*)out, ldo, J, cols)
+    const int threads = 256;
+#define BRAID_XI(T, TW) braid_launch(bias_xielu_kernel<T, TW>, dim3(rows, (cols + XIELU_SPAN - 1) / XIELU_SPAN), dim3(threads), 0, s, (const T*)z, ldz, (const TW*)b, (const TW*)pq, (T*)out, ldo, J, cols)
     if (dtype == BRAID_F32 && w_dtype == BRAID_F32) BRAID_XI(float, float);
     else if (dtype == BRAID_BF16 && w_dtype == BRAID_BF16) BRAID_XI(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == BRAID_BF16 && w_dtype == BRAID_F32) BRAID_XI(__nv_bfloat16, float);

@@ -263,7 +263,7 @@ class GQAAttention(Mixer):
         n_splits = 1
         if few:
             g = self.nqh // self.nkh
-            ctas = ctx.n_seqs * self.nkh * -(-g // 16)
+            ctas = ctx.n_seqs * self.nkh * -(-g // 16) * (value_heads // K.attn_value_heads_a_launch(hd, value_heads))
             span = min(ctx.max_kv_len, self.window + self.keep_first) if self.window else ctx.max_kv_len
             tiles = max(1, -(-span // 32))
             # one wave of CTAs over the device, and at least four key tiles a slice
