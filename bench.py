@@ -1394,7 +1394,7 @@ def ludazen_config(z):
     dense feed-forward is as wide as the experts a token uses."""
     hd = 128 if z["dim"] + z["rot"] > 64 else 64
     att = {"heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5,
-           "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+           "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
            "mask": {"size": 1024, "keep_first": 4}}
     lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "rot": {"base": 10000.0, "dims": z["rot"]},
            "vdim": z["vdim"], "kv_rank": z["rank"], "scale": (z["dim"] + z["rot"]) ** -0.5, "mask": {"size": 1024}}

@@ -78,7 +78,8 @@ def plain_talking_attention(q, keys, vals, pos, scale, temp, talk, nkh, size, ke
 
 @pytest.mark.parametrize("kernel", ["simple_f32", "simple_bf16", "mma_prompt", "mma_few_1", "mma_few_7"])
 @pytest.mark.parametrize("nqh, nkh, hd, size, keep", [(4, 2, 48, 40, 3), (6, 3, 16, 64, 0), (3, 3, 48, 7, 9), (8, 4, 64, 70, 5),
-                                                      (4, 4, 128, 96, 2), (2, 1, 64, 300, 1), (2, 2, 32, 1, 0), (4, 1, 32, 33, 70)])
+                                                      (4, 4, 128, 96, 2), (2, 1, 64, 300, 1), (2, 2, 32, 1, 0), (4, 1, 32, 33, 70),
+                                                      (3, 3, 96, 50, 4)])
 def test_attention_with_kept_first_tokens_a_factor_a_head_and_values_of_every_kv_head(K, kernel, nqh, nkh, hd, size, keep):
     """For the last query of each sequence, the keys at the window's edge (the oldest one inside, the one just outside)
     and at the kept tokens' edge (the last kept, the first not kept) stand out: their scores are far above the others
