@@ -418,6 +418,14 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bflo
     }
 }
 
+// Stages of the few-token kernel's ring: three, or two where several value tiles ride with a key tile (more CTAs an SM
+// then hide a tile's latency better than a deeper ring does).
+#if BRAID_VH > 1
+#define FEW_STAGES 2
+#else
+#define FEW_STAGES 3
+#endif
+
 template <int NW, int BN, int ST>
 static int launch_attn(const AttnMmaArgs& a, int n_seqs, int max_q_len, cudaStream_t s) {
     using C = AttnCfg<BRAID_HD, NW, BN, ST>;
@@ -455,9 +463,9 @@ extern "C" int braid_attn_mma_decode_slots(int kind) {
     int dev = 0, sms = 0, per_sm = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    using C = AttnCfg<BRAID_HD, 1, 32, 3>;
-    cudaFuncSetAttribute(attn_mma_kernel<BRAID_HD, 1, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<BRAID_HD, 1, 32, 3>, 32, C::SMEM);
+    using C = AttnCfg<BRAID_HD, 1, 32, FEW_STAGES>;
+    cudaFuncSetAttribute(attn_mma_kernel<BRAID_HD, 1, 32, FEW_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<BRAID_HD, 1, 32, FEW_STAGES>, 32, C::SMEM);
     if (e != cudaSuccess || per_sm <= 0 || sms <= 0) return 148 * 4;
     return per_sm * sms;
 }
@@ -500,7 +508,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
 #else
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
 #endif
-    else rc = launch_attn<1, 32, 3>(a, n_seqs, max_q_len, s);
+    else rc = launch_attn<1, 32, FEW_STAGES>(a, n_seqs, max_q_len, s);
     if (rc) return rc;
     // the slices merge once every value head of a row is there
     if (n_splits > 1) {
